@@ -1,0 +1,122 @@
+/* krn_b200.h — C ABI of libkrn_b200.so, the prebuilt sm_100a kernel library behind the B200 device.
+ *
+ * Every entry point is `extern "C"`, takes raw device addresses and 64-bit extents, enqueues work on the
+ * caller's CUDA stream and returns without synchronising. The return value is a status code (0 = ok);
+ * `krn_b200_last_error` gives the calling thread's message for the last non-zero status. Nothing here
+ * allocates, frees or retains caller tensors. There is no CPU fallback: on a machine without a B200 the
+ * compute entry points return KRN_B200_ERR_CUDA / KRN_B200_ERR_UNSUPPORTED.
+ *
+ * The Python host reaches this file's functions through `krn_b200.hw.Libraries` and ctypes, the way the
+ * reference reaches its compiled C programs (src/krn/runtime/cpu.py:168-175) — argument order below is the
+ * order the ctypes prototypes in krn_b200/runtime/native.py declare.
+ */
+#ifndef KRN_B200_H
+#define KRN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KRN_B200_ABI_VERSION 1
+
+/* status codes */
+#define KRN_B200_OK 0
+#define KRN_B200_ERR_INVALID_ARGUMENT 1 /* null pointer, negative extent, misaligned address or stride */
+#define KRN_B200_ERR_UNSUPPORTED 2      /* shape / dtype / device this library has no kernel for */
+#define KRN_B200_ERR_CUDA 3             /* a CUDA runtime or driver call failed; message names it */
+#define KRN_B200_ERR_WORKSPACE 4        /* caller workspace missing or too small */
+#define KRN_B200_ERR_DEVICE_TIMEOUT 5   /* a bounded device-side wait expired (read from the status word) */
+
+/* element types (operands and outputs) */
+#define KRN_B200_F32 0
+#define KRN_B200_F16 1
+#define KRN_B200_BF16 2
+#define KRN_B200_E4M3 3
+
+/* Replaces the reference's version probes of its compiled artefacts (digest of nvrtc version + flags,
+ * src/krn/runtime/cuda_backend.py:695-747): the host checks the ABI number before binding prototypes. */
+int krn_b200_version(void);
+
+/* Message for the last non-zero status returned on this thread; copies at most `size` bytes including the
+ * terminator and returns the full message length. Mirrors CUDAError's "name: message" text
+ * (src/krn/runtime/cuda_backend.py:97-105). */
+size_t krn_b200_last_error(char* buffer, size_t size);
+
+/* Device-side status word of the current device: bounded waits that expired inside a kernel leave
+ * (code, site) here instead of trapping (the reference's device wait traps after 2^26 polls,
+ * src/krn/facts/catalog.py:1439-1448). Reads and clears it. Call after the stream has been synchronised —
+ * the reference surfaces asynchronous failures at the next event the same way
+ * (src/krn/runtime/runtime.py:392-399). */
+int krn_b200_device_status(int* code, int* site, unsigned int* block);
+
+/* C[M,N] = A[M,K] * B[N,K]^T, f32 accumulation, one rounding to the output type (round to nearest even).
+ * The tile product `a[rows, ks] @ b[cols, ks].transpose()` accumulated over a `pipelined` K loop and stored
+ * with `c[rows, cols] = acc.to(T)`: replaces Builder.accumulate + Emitter.pipeline + NvidiaMma.product +
+ * emit_TileStore (src/krn/compiler/capture.py:3170-3211, src/krn/compiler/emit.py:564-672,763-774,
+ * src/krn/compiler/cuda.py:133-193).
+ *   ab_type  KRN_B200_BF16 or KRN_B200_F16 (both operands)
+ *   c_type   KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32
+ *   lda/ldb/ldc  row pitches in ELEMENTS; pitch * element size and every base address must be multiples
+ *                of 16 bytes. K == 0 stores zeros (the reference stores the untouched zero accumulator).
+ * Ragged M, N, K are handled like the reference's invalid lanes: out-of-range operand elements read as
+ * zero, out-of-range outputs are not stored (src/krn/compiler/emit.py:957-974,763-774). */
+int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                     int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* C[M,N] = sum over 128-wide K blocks kb of  sa[m,kb] * sb[n/128,kb] * (A8[m, kb] . B8[n, kb]),
+ * A8/B8 e4m3fn codes (one byte each, K-major), sa f32 [M, ceil(K/128)] (one scale per 1x128 block of A,
+ * the reference's FP8FN block format, src/krn/data/formats.py:157-164), sb f32 [ceil(N/128), ceil(K/128)]
+ * (one per 128x128 block of B). Partial sums of each K block are formed by the tensor cores and scaled
+ * when they are added to the f32 accumulator — "a coarse scale ... is applied to the partial sums outside
+ * the unit" (src/krn/facts/targets.py:127-138); operands are never dequantised in memory. Output type
+ * c_type as above. K must be a multiple of 16 (TMA pitch); lds* in elements. */
+int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b, const float* sb,
+                                     void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                     int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream);
+
+/* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (batch, q head), the statement
+ * sequence of the reference's example kernel (examples/04_libraries/08_flash_attention.py:44-59): scores
+ * carry scale_log2 = log2(e)/sqrt(d) so every exponential is exp2, masked scores take -1.0e30, running
+ * max / sum in f32, P rounded to the storage type before P·V, output (acc / l) rounded once.
+ *   q, o : [batch, q_heads, seq_q, d]    k, v : [batch, kv_heads, seq_kv, d]   (bf16, d contiguous)
+ *   q_heads % kv_heads == 0 (grouped-query attention: q head h reads kv head h / (q_heads / kv_heads))
+ *   causal != 0: key position j is visible to query position i when j <= i + (seq_kv - seq_q)
+ *   *_stride_b / *_stride_h / *_stride_s: element strides of batch, head and sequence axes.
+ * d must be 64 or 128. */
+int krn_b200_attn_fwd(int type, const void* q, const void* k, const void* v, void* o, int64_t batch, int64_t q_heads,
+                      int64_t kv_heads, int64_t seq_q, int64_t seq_kv, int64_t d, float scale_log2, int causal,
+                      const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                      const int64_t* o_strides, void* stream);
+
+/* Bytes of caller workspace krn_b200_attn_decode_fp8_paged needs for these extents (split-KV partials). */
+int64_t krn_b200_attn_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t d, int64_t max_context);
+
+/* Decode attention (one query token per sequence) over a paged e4m3 KV cache. The reference has no
+ * implementation of this (roadmap item "Paged attention"); the arithmetic follows the flash-attention
+ * statements above with K and V dequantised as code * scale.
+ *   q  bf16 [batch, q_heads, d]         o  bf16 [batch, q_heads, d]
+ *   k_pages, v_pages  e4m3 codes [num_pages, page_size, kv_heads, d]
+ *   page_table  int32 [batch, max_pages_per_seq]: page ids of each sequence in order
+ *   context_len int32 [batch]
+ *   k_scale, v_scale  f32 [batch, kv_heads]
+ *   workspace   at least krn_b200_attn_decode_workspace_bytes(...) bytes, 256-byte aligned */
+int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
+                                   const int32_t* context_len, const float* k_scale, const float* v_scale, void* o,
+                                   int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t d, int64_t page_size,
+                                   int64_t max_pages_per_seq, int64_t max_context, float scale_log2, void* workspace,
+                                   int64_t workspace_bytes, void* stream);
+
+/* Copy this rank's column block C_local[M, n_local] into columns [col0, col0 + n_local) of the row-major
+ * C_full[M, N] (ld in elements, elem_bytes 2 or 4). Used after the NCCL all-gather of GEMM output column
+ * blocks to lay the gathered slabs out as one row-major matrix. No counterpart in the reference (it has no
+ * multi-device path). */
+int krn_b200_scatter_columns(const void* slabs, void* c_full, int64_t m, int64_t n_local, int64_t ranks,
+                             int64_t ld_full, int elem_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KRN_B200_H */

@@ -1,0 +1,442 @@
+// C[M,N] = A[M,K] * B[N,K]^T for 16-bit operands (bf16 / f16), f32 accumulation in tensor memory.
+//
+// One persistent, warp-specialised kernel per CTA-pair mode:
+//   warp 0      TMA producer: one lane streams 128-byte-swizzled A and B tiles into a ring of shared-memory
+//               stages and arms the stage's "full" mbarrier with the byte count;
+//   warp 1      MMA issuer: one lane waits for "full", issues four tcgen05.mma (K = 16 each) per stage
+//               into one of two tensor-memory accumulators and commits the stage's "empty" barrier;
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns 32 lanes = 32 rows), round
+//               to the output type, stage 32x(128 byte) boxes in swizzled shared memory and TMA-store them,
+//               while the MMA warp already fills the other accumulator with the next tile.
+// In pair mode (CTA_GROUP = 2) two CTAs on one TPC form a cluster and share a 256x256 output tile: each
+// loads its own 128 rows of A and its own 128 of the tile's 256 B rows (no multicast — every byte is
+// fetched once by exactly one CTA), the leader issues cta_group::2 MMAs that read both CTAs' shared memory
+// and write both CTAs' tensor memory, and barrier arrivals cross the pair through the cluster window.
+//
+// This is the lowering of `acc += a[rows, ks] @ b[cols, ks].transpose()` in a `pipelined` loop followed by
+// `c[rows, cols] = acc.to(T)`; the reference lowers it to mma.sync + ldmatrix + a cp.async ring
+// (src/krn/compiler/cuda.py:133-193, src/krn/compiler/emit.py:564-672) and stores with per-element guards
+// (src/krn/compiler/emit.py:763-774). TMA gives the same ragged-edge semantics: out-of-range operand
+// elements arrive as zeros, out-of-range output elements are clipped.
+#include "host.cuh"
+
+#include <cstdlib>
+
+namespace krnb {
+namespace {
+
+constexpr int kBM = 128;          // rows of C per CTA = tensor-memory lanes
+constexpr int kBN = 256;          // columns of C per tile = UMMA N
+constexpr int kRowBytes = 128;    // bytes of K per stage row (one swizzle span)
+constexpr int kThreads = 192;
+constexpr int kTmemColumns = 512; // two 256-column f32 accumulators
+
+template <int CTA_GROUP>
+struct Layout {
+  static constexpr int kBRows = kBN / CTA_GROUP;
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = kBRows * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = CTA_GROUP == 2 ? 6 : 4;
+  static constexpr int kEpilogueBytes = 4 * 2 * 4096;  // 4 warps x 2 buffers x (32 rows x 128 bytes)
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
+};
+
+struct Problem {
+  int m, n, k;
+  int tiles_m, tiles_n;
+};
+
+// Tile order: bands of 8 tile rows walked column by column, so that the tiles in flight at any time
+// share a few A row-panels and B column-panels in L2.
+__device__ __forceinline__ void tile_coords(int t, const Problem& p, int& tm, int& tn) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * p.tiles_n;
+  const int band = t / per_band;
+  const int first = band * kBand;
+  const int height = min(kBand, p.tiles_m - first);
+  const int r = t - band * per_band;
+  tm = first + r % height;
+  tn = r / height;
+}
+
+enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
+
+template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, Problem p, uint32_t ab_format, DeviceStatus* status) {
+  using L = Layout<CTA_GROUP>;
+  constexpr int kBK = kRowBytes / ELEM_BYTES;                 // K elements per stage
+  constexpr int kChunkCols = kRowBytes / int(sizeof(OutT));   // output columns per 128-byte store row
+  constexpr int kChunks = kBN / kChunkCols;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t stages_addr = base;
+  const uint32_t epilogue_addr = base + L::kStages * L::kStageBytes;
+  uint8_t* tail = smem + L::kStages * L::kStageBytes + L::kEpilogueBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+  const uint32_t full_bar = smem_u32(bars);                       // [kStages]
+  const uint32_t empty_bar = full_bar + 8 * L::kStages;           // [kStages]
+  const uint32_t tmem_full_bar = empty_bar + 8 * L::kStages;      // [2]
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16;             // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * L::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const uint32_t rank = CTA_GROUP == 2 ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / CTA_GROUP;
+  const int num_clusters = gridDim.x / CTA_GROUP;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full_bar + 8 * i, 1);
+      mbar_init(tmem_empty_bar + 8 * i, 4 * CTA_GROUP);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
+    tmem_relinquish<CTA_GROUP>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        const int row_a = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
+        const int row_b = tn * kBN + int(rank) * L::kBRows;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stages_addr + stage * L::kStageBytes;
+          const uint32_t b_dst = a_dst + L::kABytes;
+          if constexpr (CTA_GROUP == 1) {
+            mbar_arrive_expect_tx(full_bar + 8 * stage, L::kStageBytes);
+            tma_load_2d(a_dst, &map_a, kb * kBK, row_a, full_bar + 8 * stage);
+            tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
+          } else {
+            // Both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both.
+            if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * L::kStageBytes);
+            const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+            tma_load_2d_pair(a_dst, &map_a, kb * kBK, row_a, leader_full);
+            tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
+          }
+          if (++stage == L::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(ab_format, ab_format, kBM * CTA_GROUP, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = stages_addr + stage * L::kStageBytes;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::kABytes);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            // 32 bytes of K per instruction: step the 16-byte-unit start address inside the swizzle span
+            umma_ss<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
+                                                (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          if constexpr (CTA_GROUP == 1) {
+            umma_commit(empty_bar + 8 * stage);
+          } else {
+            umma_commit_pair(empty_bar + 8 * stage, 0x3);
+          }
+          if (++stage == L::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if constexpr (CTA_GROUP == 1) {
+          umma_commit(tmem_full_bar + 8 * acc);
+        } else {
+          umma_commit_pair(tmem_full_bar + 8 * acc, 0x3);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int quarter = warp & 3;  // the 32-lane slice of tensor memory this warp may read
+    const uint32_t my_buffers = epilogue_addr + quarter * 2 * 4096;
+    const uint32_t leader_tmem_empty = CTA_GROUP == 2 ? map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
+    int iter = 0;
+    bool ok = true;
+    int stores = 0;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      const int row0 = tm * (kBM * CTA_GROUP) + int(rank) * kBM + quarter * 32;
+      const int col0 = tn * kBN;
+      // warp-uniform verdict: the aligned tensor-memory loads below need all 32 lanes together
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, status, kSiteEpilogueFull))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
+        const int col = col0 + chunk * kChunkCols;
+        const bool live = row0 < p.m && col < p.n;  // warp-uniform
+        uint32_t packed[32];
+        if constexpr (sizeof(OutT) == 4) {
+          tmem_ld_32x32(t_row + chunk * kChunkCols, packed);
+          tmem_ld_wait();
+        } else {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
+          tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if constexpr (OUT_BF16) {
+              packed[i] = pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[16 + i] = pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+            } else {
+              packed[i] = pack_f16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[16 + i] = pack_f16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+            }
+          }
+        }
+        if (live) {
+          const uint32_t buffer = my_buffers + (stores & 1) * 4096;
+          // the store issued two stores ago read this buffer; wait until it has
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          const uint32_t row_addr = buffer + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
+                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                         : "memory");
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_c, col, row0, buffer);
+            tma_store_commit();
+          }
+          ++stores;
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTA_GROUP == 2) {
+          mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
+        } else {
+          mbar_arrive(tmem_empty_bar + 8 * acc);
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    // abandoned: give this CTA's own copies in flight time to land before shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CTA_GROUP>(tmem_base, kTmemColumns);
+  }
+}
+
+template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
+           uint32_t fmt, cudaStream_t stream) {
+  using L = Layout<CTA_GROUP>;
+  auto kernel = gemm_tn_kernel<CTA_GROUP, 2, OutT, OUT_BF16>;
+  KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
+  const int tiles = p.tiles_m * p.tiles_n;
+  int clusters = ctx->sm_count / CTA_GROUP;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(clusters * CTA_GROUP), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = L::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA_GROUP;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, fmt, ctx->status_dev));
+  return KRN_B200_OK;
+}
+
+__global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitch_bytes, long long rows) {
+  const long long total = rows * row_bytes;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    c[(i / row_bytes) * pitch_bytes + i % row_bytes] = 0;
+  }
+}
+
+}  // namespace
+
+// Pair mode can be switched off for experiments (KRN_B200_GEMM_PAIR=0); by default it is used whenever
+// the problem has more than one 128-row panel.
+int gemm_pair_mode(int64_t m) {
+  static int env = [] {
+    const char* v = getenv("KRN_B200_GEMM_PAIR");
+    return v == nullptr ? -1 : atoi(v);
+  }();
+  if (env == 0) return 1;
+  if (env == 1) return 2;
+  return m > kBM ? 2 : 1;
+}
+
+}  // namespace krnb
+
+extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
+                                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
+    return fail(KRN_B200_ERR_UNSUPPORTED,
+                "operand type %d is not available on sm_100a: this entry point multiplies 16-bit tiles. "
+                "Instead: pass KRN_B200_BF16 or KRN_B200_F16 (FP8 has its own entry point)", ab_type);
+  }
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
+  }
+  if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent (%lld, %lld, %lld)",
+                                           (long long)m, (long long)n, (long long)k);
+  if (m == 0 || n == 0) return KRN_B200_OK;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
+  }
+  if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr))) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  if (ldc < n || (k > 0 && (lda < k || ldb < k))) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row (lda %lld, ldb %lld, ldc %lld)",
+                (long long)lda, (long long)ldb, (long long)ldc);
+  }
+  DeviceContext* ctx = current_context();
+  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
+  if (int rc = require_sm100(ctx)) return rc;
+
+  if (k == 0) {
+    // the zero accumulator is stored untouched (src/krn/compiler/emit.py:739-755)
+    zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(static_cast<uint8_t*>(c), n * c_bytes, ldc * c_bytes, m);
+    KRNB_CUDA(cudaGetLastError());
+    return KRN_B200_OK;
+  }
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 ||
+      (ldc * c_bytes) % 16 != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT,
+                "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld, ldc %lld elements)",
+                (long long)lda, (long long)ldb, (long long)ldc);
+  }
+
+  const int group = gemm_pair_mode(m);
+  Problem p;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
+  p.tiles_n = int((n + kBN - 1) / kBN);
+
+  const CUtensorMapDataType ab_dt = ab_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_a, map_b, map_c;
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(lda) * 2};
+    uint32_t box[2] = {64, uint32_t(kBM)};
+    if (int rc = encode_tensor_map(&map_a, ab_dt, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
+    uint64_t strides[1] = {uint64_t(ldb) * 2};
+    uint32_t box[2] = {64, uint32_t(kBN / group)};
+    if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  const uint32_t fmt = ab_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
+  if (group == 2) {
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, fmt, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+  }
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, fmt, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+}

@@ -1,0 +1,114 @@
+"""Typed Python calls over the C ABI for callers that already hold device memory (torch tensors or this
+package's device tensors): shape checks, pitch extraction, status → exception. Nothing here computes; a
+missing kernel library raises `LibraryNotFound`."""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+from krn_b200.runtime import native
+
+_ELEMENT = {"bfloat16": native.BF16, "float16": native.F16, "float32": native.F32, "float8_e4m3fn": native.E4M3,
+            "uint8": native.E4M3}
+
+
+def _type_of(tensor: Any) -> int:
+    name = str(getattr(tensor, "dtype", "")).replace("torch.", "")
+    if name not in _ELEMENT:
+        raise TypeError(f"no kernel element type for {name!r}")
+    return _ELEMENT[name]
+
+
+def _pointer(tensor: Any) -> int:
+    if hasattr(tensor, "data_ptr"):
+        return int(tensor.data_ptr())
+    return int(tensor.pointer)
+
+
+def _pitch(tensor: Any) -> int:
+    """Row pitch in elements of a rank-2 tensor whose last axis is contiguous."""
+    strides = tuple(tensor.stride()) if callable(getattr(tensor, "stride", None)) else tuple(tensor.strides)
+    if len(strides) != 2 or (tensor.shape[1] > 1 and strides[1] != 1):
+        raise ValueError("expected a rank-2 tensor with a contiguous last axis")
+    return int(strides[0]) if tensor.shape[0] > 1 else max(int(strides[0]), int(tensor.shape[1]))
+
+
+def _stream(stream: Any) -> ctypes.c_void_p:
+    if stream is None:
+        return ctypes.c_void_p(0)
+    if hasattr(stream, "cuda_stream"):
+        return ctypes.c_void_p(int(stream.cuda_stream))
+    if hasattr(stream, "__cuda_stream__"):
+        return ctypes.c_void_p(int(stream.__cuda_stream__()[1]))
+    return ctypes.c_void_p(int(stream))
+
+
+def gemm_tn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
+    """c[M, N] = a[M, K] @ b[N, K]^T with f32 accumulation; a, b bf16 or f16 (same type), c bf16/f16/f32."""
+    (m, k), (n, kb) = a.shape, b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    if _type_of(a) != _type_of(b):
+        raise TypeError("both operands must have the same element type")
+    status = native.library().krn_b200_gemm_tn(
+        _type_of(a), _type_of(c), _pointer(a), _pointer(b), _pointer(c), m, n, k, _pitch(a), _pitch(b), _pitch(c),
+        _stream(stream))
+    native.check(status, "tile matrix product")
+
+
+def gemm_fp8_blockscaled_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: Any = None) -> None:
+    """c = sum_kb sa[:, kb] * sb[n // 128, kb] * (a8[:, kb] @ b8[:, kb]^T); a, b e4m3 codes, scales f32."""
+    (m, k), (n, kb) = a.shape, b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    blocks = -(-k // 128)
+    if tuple(sa.shape) != (m, blocks) or tuple(sb.shape) != (-(-n // 128), blocks):
+        raise ValueError(f"scale shapes {tuple(sa.shape)}, {tuple(sb.shape)} do not match 1x128 / 128x128 blocks")
+    status = native.library().krn_b200_gemm_fp8_blockscaled_tn(
+        _type_of(c), _pointer(a), _pointer(sa), _pointer(b), _pointer(sb), _pointer(c), m, n, k, _pitch(a), _pitch(b),
+        _pitch(c), _pitch(sa), _pitch(sb), _stream(stream))
+    native.check(status, "block-scaled FP8 tile matrix product")
+
+
+def _strides3(tensor: Any) -> Any:
+    strides = tuple(tensor.stride()) if callable(getattr(tensor, "stride", None)) else tuple(tensor.strides)
+    if len(strides) != 4 or strides[3] != 1:
+        raise ValueError("expected a rank-4 tensor [batch, heads, seq, d] with a contiguous last axis")
+    return (ctypes.c_int64 * 3)(*strides[:3])
+
+
+def attention_forward(q: Any, k: Any, v: Any, o: Any, scale_log2: float, causal: bool, stream: Any = None) -> None:
+    """o = softmax(scale * q k^T [+ causal mask]) v per (batch, q head); scores carry scale_log2 = log2(e) * scale."""
+    batch, hq, sq, d = q.shape
+    _, hkv, skv, _ = k.shape
+    status = native.library().krn_b200_attn_fwd(
+        _type_of(q), _pointer(q), _pointer(k), _pointer(v), _pointer(o), batch, hq, hkv, sq, skv, d, scale_log2,
+        int(causal), _strides3(q), _strides3(k), _strides3(v), _strides3(o), _stream(stream))
+    native.check(status, "flash attention forward")
+
+
+def decode_workspace_bytes(batch: int, q_heads: int, d: int, max_context: int) -> int:
+    return int(native.library().krn_b200_attn_decode_workspace_bytes(batch, q_heads, d, max_context))
+
+
+def attention_decode_fp8_paged(q: Any, k_pages: Any, v_pages: Any, page_table: Any, context_len: Any, k_scale: Any,
+                               v_scale: Any, o: Any, scale_log2: float, max_context: int, workspace: Any,
+                               stream: Any = None) -> None:
+    batch, hq, d = q.shape
+    _, page_size, hkv, _ = k_pages.shape
+    nbytes = workspace.numel() * workspace.element_size() if hasattr(workspace, "numel") else workspace.nbytes
+    status = native.library().krn_b200_attn_decode_fp8_paged(
+        _pointer(q), _pointer(k_pages), _pointer(v_pages), _pointer(page_table), _pointer(context_len),
+        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, page_table.shape[1],
+        max_context, scale_log2, _pointer(workspace), nbytes, _stream(stream))
+    native.check(status, "paged FP8 decode attention")
+
+
+def scatter_columns(slabs: Any, c_full: Any, ranks: int, stream: Any = None) -> None:
+    """slabs [ranks, M, n_local] -> c_full [M, ranks * n_local] (row-major)."""
+    _, m, n_local = slabs.shape
+    element = c_full.element_size() if hasattr(c_full, "element_size") else c_full.itemsize
+    status = native.library().krn_b200_scatter_columns(_pointer(slabs), _pointer(c_full), m, n_local, ranks,
+                                                       _pitch(c_full), element, _stream(stream))
+    native.check(status, "column scatter")
