@@ -1,5 +1,440 @@
-#include "host.cuh"
-extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int, const void*, const float*, const void*, const float*, void*, int64_t,
-                                                int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, void*) {
-  return krnb::fail(KRN_B200_ERR_UNSUPPORTED, "block-scaled FP8 product: kernel not built yet");
+// Block-scaled FP8 tile product:
+//   C[m,n] = sum over 128-wide K blocks kb of  sa[m,kb] * sb[n/128,kb] * (A8[m,kb-block] . B8[n,kb-block])
+// A8, B8 are e4m3fn codes (K-major), sa has one f32 per 1x128 block of A, sb one per 128x128 block of B.
+//
+// One 128-byte swizzle row of an FP8 operand is exactly one scale block (128 codes), so one pipeline stage is
+// one K block. The tensor cores form the UNSCALED partial product of a stage in tensor memory
+// (tcgen05.mma kind::f8f6f4, four K=32 instructions, accumulate flag cleared on the first), and while they
+// work on the next stage into the other partial buffer the promotion warps read the finished partial
+// (tcgen05.ld) and fold it into f32 accumulators held in registers with one packed fma per pair of
+// elements: acc += (sa[row,kb] * sb[block,kb]) * partial. The scale therefore rides on the accumulation of
+// partial sums — "a coarse scale is applied to the partial sums outside the unit"
+// (src/krn/facts/targets.py:127-138) — and no dequantised copy of an operand ever exists. The reference has
+// no implementation of this product (QMatrix / QTile are signatures only, src/krn/frontend/memory.py:173-193).
+//
+// Roles per CTA (384 threads = 3 warpgroups): warp 0 TMA producer, warp 1 MMA issuer (warps 2, 3 idle; the
+// group gives its registers away with setmaxnreg), warps 4..11 promotion + store with 232 registers each. A
+// promotion warp owns 32 rows (its tensor-memory lane quarter) x 128 columns (one scale block of B), i.e.
+// 128 accumulators per thread. In pair mode two CTAs share a 256x256 tile exactly as the 16-bit kernel does
+// (each loads its own operand halves; no multicast).
+#include "gemm_common.cuh"
+
+#include <cstdlib>
+
+namespace krnb {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 128;  // FP8 codes per stage row = one scale block
+constexpr int kThreads = 384;  // three warpgroups: {producer, MMA, 2 idle}, promotion x 2
+constexpr int kPromotionWarps = 8;
+constexpr int kTmemColumns = 512;  // two 256-column partial accumulators
+
+template <int CTA_GROUP>
+struct Layout {
+  static constexpr int kBRows = kBN / CTA_GROUP;
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBBytes = kBRows * 128;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = CTA_GROUP == 2 ? 5 : 3;
+  static constexpr int kStoreBytes = kPromotionWarps * 8192;  // per warp: 32 rows x 256 bytes
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;
+};
+
+struct Scales {
+  const float* sa;
+  const float* sb;
+  long long ldsa, ldsb;
+  int blocks_n;  // ceil(N / 128)
+};
+
+enum Site { kSiteProducerEmpty = 11, kSiteMmaFull = 12, kSiteMmaPartialEmpty = 13, kSitePromotionFull = 14 };
+
+__device__ __forceinline__ void fma_chunk(float2 (&acc)[64], int chunk, const uint32_t (&p)[32], float scale) {
+  const float2 s2 = make_float2(scale, scale);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 v = make_float2(__uint_as_float(p[2 * i]), __uint_as_float(p[2 * i + 1]));
+    acc[chunk * 16 + i] = __ffma2_rn(v, s2, acc[chunk * 16 + i]);
+  }
+}
+
+template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, Problem p, Scales scales, DeviceStatus* status) {
+  using L = Layout<CTA_GROUP>;
+  constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t stages_addr = base;
+  const uint32_t store_addr = base + L::kStages * L::kStageBytes;
+  uint8_t* tail = smem + L::kStages * L::kStageBytes + L::kStoreBytes;
+  const uint32_t full_bar = smem_u32(tail);
+  const uint32_t empty_bar = full_bar + 8 * L::kStages;
+  const uint32_t part_full_bar = empty_bar + 8 * L::kStages;
+  const uint32_t part_empty_bar = part_full_bar + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * L::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const uint32_t rank = CTA_GROUP == 2 ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / CTA_GROUP;
+  const int num_clusters = gridDim.x / CTA_GROUP;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(part_full_bar + 8 * i, 1);
+      mbar_init(part_empty_bar + 8 * i, kPromotionWarps * CTA_GROUP);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
+    tmem_relinquish<CTA_GROUP>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) reg_dealloc<48>();
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        const int row_a = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
+        const int row_b = tn * kBN + int(rank) * L::kBRows;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stages_addr + stage * L::kStageBytes;
+          const uint32_t b_dst = a_dst + L::kABytes;
+          if constexpr (CTA_GROUP == 1) {
+            mbar_arrive_expect_tx(full_bar + 8 * stage, L::kStageBytes);
+            tma_load_2d(a_dst, &map_a, kb * kBK, row_a, full_bar + 8 * stage);
+            tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
+          } else {
+            if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * L::kStageBytes);
+            const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+            tma_load_2d_pair(a_dst, &map_a, kb * kBK, row_a, leader_full);
+            tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
+          }
+          if (++stage == L::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(kFmtE4M3, kFmtE4M3, kBM * CTA_GROUP, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t it = 0;  // K blocks issued so far, over all tiles: selects the partial buffer
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t buf = it & 1u;
+          if (!mbar_wait(part_empty_bar + 8 * buf, ((it >> 1) & 1u) ^ 1u, abort_flag, status, kSiteMmaPartialEmpty) ||
+              !mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * kBN;
+          const uint32_t a_addr = stages_addr + stage * L::kStageBytes;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::kABytes);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_ss<CTA_GROUP, true>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+          }
+          if constexpr (CTA_GROUP == 1) {
+            umma_commit(empty_bar + 8 * stage);
+            umma_commit(part_full_bar + 8 * buf);
+          } else {
+            umma_commit_pair(empty_bar + 8 * stage, 0x3);
+            umma_commit_pair(part_full_bar + 8 * buf, 0x3);
+          }
+          if (++stage == L::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- promotion + store warps
+    reg_alloc<232>();
+    const int pw = warp - 4;       // 0..7
+    const int quarter = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int half = pw >> 2;      // which 128-column scale block of the tile
+    const uint32_t my_store = store_addr + pw * 8192;
+    const uint32_t leader_part_empty = CTA_GROUP == 2 ? map_to_cta(part_empty_bar, 0) : part_empty_bar;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      const int row0 = tm * (kBM * CTA_GROUP) + int(rank) * kBM + quarter * 32;
+      const int col0 = tn * kBN + half * 128;
+      const int row = row0 + int(lane);
+      const bool row_ok = row < p.m;
+      const int nb = col0 / 128;
+      const bool nb_ok = nb < scales.blocks_n;
+      const float* sa_row = scales.sa + (long long)(row_ok ? row : 0) * scales.ldsa;
+      const float* sb_row = scales.sb + (long long)(nb_ok ? nb : 0) * scales.ldsb;
+
+      float2 acc[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+
+      float next_scale = (num_kb > 0 && row_ok && nb_ok) ? __ldg(sa_row) * __ldg(sb_row) : 0.f;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const uint32_t buf = it & 1u;
+        const float scale = next_scale;
+        if (kb + 1 < num_kb && row_ok && nb_ok) next_scale = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
+        if (!__all_sync(0xffffffffu,
+                        mbar_wait(part_full_bar + 8 * buf, (it >> 1) & 1u, abort_flag, status, kSitePromotionFull))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kBN + half * 128;
+        uint32_t p0[32], p1[32];
+        tmem_ld_32x32(t_addr, p0);
+        tmem_ld_wait(p0);
+        tmem_ld_32x32(t_addr + 32, p1);
+        fma_chunk(acc, 0, p0, scale);
+        tmem_ld_wait(p1);
+        tmem_ld_32x32(t_addr + 64, p0);
+        fma_chunk(acc, 1, p1, scale);
+        tmem_ld_wait(p0);
+        tmem_ld_32x32(t_addr + 96, p1);
+        fma_chunk(acc, 2, p0, scale);
+        tmem_ld_wait(p1);
+        // the partial buffer is fully read: hand it back before the last fmas
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTA_GROUP == 2) {
+            mbar_arrive_cluster(leader_part_empty + 8 * buf);
+          } else {
+            mbar_arrive(part_empty_bar + 8 * buf);
+          }
+        }
+        fma_chunk(acc, 3, p1, scale);
+      }
+      if (!ok) break;
+
+      // ---- store this warp's 32 x 128 block: 128-byte rows through swizzled shared memory and TMA
+      constexpr int kStoreChunks = 128 / kChunkCols;        // 2 for 16-bit outputs, 4 for f32
+      constexpr int kChunksPerRound = 2;                     // 8 KB of staging = two 32 x 128-byte boxes
+#pragma unroll
+      for (int round = 0; round < kStoreChunks / kChunksPerRound; ++round) {
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < kChunksPerRound; ++c) {
+          const int chunk = round * kChunksPerRound + c;
+          uint32_t packed[32];
+          if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              packed[2 * i] = __float_as_uint(acc[chunk * 16 + i].x);
+              packed[2 * i + 1] = __float_as_uint(acc[chunk * 16 + i].y);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float2 v = acc[chunk * 32 + i];
+              packed[i] = OUT_BF16 ? pack_bf16x2(v.x, v.y) : pack_f16x2(v.x, v.y);
+            }
+          }
+          const uint32_t row_addr = my_store + c * 4096 + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
+                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                         : "memory");
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int c = 0; c < kChunksPerRound; ++c) {
+            const int col = col0 + (round * kChunksPerRound + c) * kChunkCols;
+            if (row0 < p.m && col < p.n) tma_store_2d(&map_c, col, row0, my_store + c * 4096);
+          }
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CTA_GROUP>(tmem_base, kTmemColumns);
+  }
+}
+
+template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
+           Scales scales, cudaStream_t stream) {
+  using L = Layout<CTA_GROUP>;
+  auto kernel = gemm_fp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
+  KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
+  const int tiles = p.tiles_m * p.tiles_n;
+  int clusters = ctx->sm_count / CTA_GROUP;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(clusters * CTA_GROUP), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = L::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA_GROUP;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, scales, ctx->status_dev));
+  return KRN_B200_OK;
+}
+
+__global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitch_bytes, long long rows) {
+  const long long total = rows * row_bytes;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    c[(i / row_bytes) * pitch_bytes + i % row_bytes] = 0;
+  }
+}
+
+}  // namespace
+}  // namespace krnb
+
+extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b,
+                                                const float* sb, void* c, int64_t m, int64_t n, int64_t k,
+                                                int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                                                void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
+  }
+  if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent");
+  if (m == 0 || n == 0) return KRN_B200_OK;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
+  }
+  if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr || sa == nullptr || sb == nullptr))) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  const int64_t blocks_k = (k + 127) / 128;
+  if (ldc < n || (k > 0 && (lda < k || ldb < k || ldsa < blocks_k || ldsb < blocks_k))) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
+  }
+  DeviceContext* ctx = current_context();
+  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
+  if (int rc = require_sm100(ctx)) return rc;
+  if (k == 0) {
+    zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(static_cast<uint8_t*>(c), n * c_bytes, ldc * c_bytes, m);
+    KRNB_CUDA(cudaGetLastError());
+    return KRN_B200_OK;
+  }
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT,
+                "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld bytes, ldc %lld elements)",
+                (long long)lda, (long long)ldb, (long long)ldc);
+  }
+  const int group = m > kBM ? 2 : 1;
+  Problem p;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
+  p.tiles_n = int((n + kBN - 1) / kBN);
+  Scales scales;
+  scales.sa = sa;
+  scales.sb = sb;
+  scales.ldsa = ldsa;
+  scales.ldsb = ldsb;
+  scales.blocks_n = int((n + 127) / 128);
+
+  CUtensorMap map_a, map_b, map_c;
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(lda)};
+    uint32_t box[2] = {128, uint32_t(kBM)};
+    if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
+    uint64_t strides[1] = {uint64_t(ldb)};
+    uint32_t box[2] = {128, uint32_t(kBN / group)};
+    if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  if (group == 2) {
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  }
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
 }

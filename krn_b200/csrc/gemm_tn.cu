@@ -18,7 +18,7 @@
 // (src/krn/compiler/cuda.py:133-193, src/krn/compiler/emit.py:564-672) and stores with per-element guards
 // (src/krn/compiler/emit.py:763-774). TMA gives the same ragged-edge semantics: out-of-range operand
 // elements arrive as zeros, out-of-range output elements are clipped.
-#include "host.cuh"
+#include "gemm_common.cuh"
 
 #include <cstdlib>
 
@@ -42,24 +42,6 @@ struct Layout {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
 };
-
-struct Problem {
-  int m, n, k;
-  int tiles_m, tiles_n;
-};
-
-// Tile order: bands of 8 tile rows walked column by column, so that the tiles in flight at any time
-// share a few A row-panels and B column-panels in L2.
-__device__ __forceinline__ void tile_coords(int t, const Problem& p, int& tm, int& tn) {
-  constexpr int kBand = 8;
-  const int per_band = kBand * p.tiles_n;
-  const int band = t / per_band;
-  const int first = band * kBand;
-  const int height = min(kBand, p.tiles_m - first);
-  const int r = t - band * per_band;
-  tm = first + r % height;
-  tn = r / height;
-}
 
 enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
 
@@ -236,12 +218,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t packed[32];
         if constexpr (sizeof(OutT) == 4) {
           tmem_ld_32x32(t_row + chunk * kChunkCols, packed);
-          tmem_ld_wait();
+          tmem_ld_wait(packed);
         } else {
           uint32_t lo[32], hi[32];
           tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
-          tmem_ld_wait();
+          tmem_ld_wait(lo, hi);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             if constexpr (OUT_BF16) {
