@@ -15,8 +15,13 @@
 // Roles per CTA (384 threads = 3 warpgroups): warp 0 TMA producer, warp 1 MMA issuer (warps 2, 3 idle; the
 // group gives its registers away with setmaxnreg), warps 4..11 promotion + store with 232 registers each. A
 // promotion warp owns 32 rows (its tensor-memory lane quarter) x 128 columns (one scale block of B), i.e.
-// 128 accumulators per thread. In pair mode two CTAs share a 256x256 tile exactly as the 16-bit kernel does
-// (each loads its own operand halves; no multicast).
+// 128 accumulators per thread.
+//
+// The hand-off between the MMA warp and the promotion warps happens every K block, so its latency decides the
+// throughput. Measured on B200 at M=8192, N=28672, K=8192: one CTA per tile (cta_group::1) 2.35 ms; CTA pairs
+// (cta_group::2, kept below as a template instance) 3.98 ms, because every hand-off then crosses the cluster;
+// splitting a stage into two N=128 halves over four partial buffers 4.26 ms, because A is then read from
+// shared memory twice per stage. The dispatch therefore uses one CTA per tile and two 256-column partials.
 #include "gemm_common.cuh"
 
 #include <cstdlib>
@@ -119,7 +124,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) reg_dealloc<48>();
+  if (warp < 4) reg_dealloc<40>();
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -328,6 +333,14 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_fp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
+  // setmaxnreg.inc blocks until the CTA's register pool holds what it asks for: refuse to launch a build
+  // whose launch-time allocation cannot cover 2 x 128 x (232 - R) with 128 x (R - 40).
+  cudaFuncAttributes attributes;
+  KRNB_CUDA(cudaFuncGetAttributes(&attributes, kernel));
+  if ((attributes.numRegs - 40) * 128 < (232 - attributes.numRegs) * 256) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "FP8 kernel was built with %d registers per thread; the register "
+                "re-partitioning needs at least 168", attributes.numRegs);
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / CTA_GROUP;
   if (clusters > tiles) clusters = tiles;
@@ -393,7 +406,7 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
                 "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld bytes, ldc %lld elements)",
                 (long long)lda, (long long)ldb, (long long)ldc);
   }
-  const int group = m > kBM ? 2 : 1;
+  const int group = 1;  // see the measurements at the top of this file
   Problem p;
   p.m = int(m);
   p.n = int(n);
@@ -429,10 +442,8 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
     uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  if (group == 2) {  // not dispatched today; kept compiling so the measurement above can be repeated
     if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
   }
   if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
   if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);

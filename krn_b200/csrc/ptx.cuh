@@ -66,6 +66,11 @@ __device__ __forceinline__ void cluster_wait() {
 }
 
 // Warpgroup-wide register re-partitioning (all four warps of a warpgroup must execute it).
+// CAUTION: `inc` blocks until the registers exist in the CTA's pool, and the pool is what the launch
+// allocated (registers per thread reported by ptxas x threads), not the whole register file. The
+// decreases must free at least what the increases ask for, or the kernel never proceeds: with 384 threads
+// launched at 168 registers, one warpgroup dropping to 40 frees 128 x 128 = 16384 registers, exactly what two
+// warpgroups rising to 232 need (256 x 64).
 template <int N>
 __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>
