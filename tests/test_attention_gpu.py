@@ -1,0 +1,121 @@
+"""Flash-attention forward on the GPU, through the C ABI, against the CPU oracle (the reference example's
+statement sequence) and the reference's own float64 check.
+
+Batched and grouped-query attention are extensions the reference does not have: for those shapes the oracle's
+definition is ours (parity unpinned); single-batch, equal-head cases follow the reference example exactly."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+
+from oracle import oracle as o
+from krn_b200.runtime import calls
+
+pytestmark = pytest.mark.gpu
+
+
+def draw(shape, dtype: str, rng) -> np.ndarray:
+    x = rng.standard_normal(shape).astype(np.float32)
+    return o.bf16_words(x) if dtype == "bf16" else x.astype(np.float16).view(np.uint16)
+
+
+def values(words: np.ndarray, dtype: str) -> np.ndarray:
+    return o.bf16_values(words) if dtype == "bf16" else words.view(np.float16).astype(np.float32)
+
+
+def run(torch, q, k, v, dtype: str, causal: bool) -> np.ndarray:
+    tdtype = torch.bfloat16 if dtype == "bf16" else torch.float16
+    dq, dk, dv = (torch.from_numpy(x.view(np.int16)).cuda().view(tdtype) for x in (q, k, v))
+    out = torch.full(dq.shape, float("nan"), device="cuda", dtype=tdtype)
+    d = q.shape[-1]
+    calls.attention_forward(dq, dk, dv, out, math.log2(math.e) / math.sqrt(d), causal)
+    torch.cuda.synchronize()
+    return out.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+CASES = [(1, 1, 1, 128, 128), (1, 2, 1, 256, 128), (2, 4, 2, 384, 128), (1, 2, 2, 200, 64), (1, 1, 1, 40, 64),
+         (1, 4, 1, 1000, 128), (1, 2, 2, 16, 128), (1, 1, 1, 1, 64), (2, 8, 2, 513, 128), (1, 2, 1, 300, 64)]
+
+
+@pytest.mark.parametrize("batch,hq,hkv,seq,d", CASES)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_attention_against_oracle_and_float64(cuda, batch, hq, hkv, seq, d, causal, dtype) -> None:
+    rng = np.random.default_rng(seq * 7 + hq)
+    q = draw((batch, hq, seq, d), dtype, rng)
+    k, v = (draw((batch, hkv, seq, d), dtype, rng) for _ in range(2))
+    got = values(run(cuda, q, k, v, dtype, causal), dtype)
+    assert np.isfinite(got).all()
+    want = values(o.flash_attention(q, k, v, dtype=o.BF16 if dtype == "bf16" else o.F16,
+                                    scale=math.log2(math.e) / math.sqrt(d), causal=causal, bq=16, bk=16, threads=8), dtype)
+    exact = o.attention_f64(values(q, dtype), values(k, dtype), values(v, dtype), causal)
+    # the benchmark's tolerance (1e-2 relative Frobenius vs an fp32-or-better oracle) and the reference's
+    # elementwise check (atol 3e-3 for f16, tests/frontend/test_tile_ops.py:130-154; bf16 has 8 fewer bits)
+    assert o.rel_frobenius(got, exact) < 1e-2
+    assert o.rel_frobenius(got, want) < 1e-2
+    np.testing.assert_allclose(got, exact, atol=3e-3 if dtype == "f16" else 2.5e-2)
+
+
+def test_reference_example_case(cuda) -> None:
+    """2 heads, 200 tokens, d in {64, 128}, f16, atol 2e-3 (examples/04_libraries/08_flash_attention.py:72-86)."""
+    rng = np.random.default_rng(0)
+    for d, causal in ((64, False), (128, True)):
+        q, k, v = (rng.standard_normal((1, 2, 200, d)).astype(np.float16) for _ in range(3))
+        got = run(cuda, *(x.view(np.uint16) for x in (q, k, v)), "f16", causal).view(np.float16).astype(np.float64)
+        np.testing.assert_allclose(got, o.attention_f64(q, k, v, causal), atol=2e-3)
+
+
+def test_strided_views_and_untouched_padding(cuda) -> None:
+    """Tensors given as views of larger allocations: strides are honoured and nothing outside O is written."""
+    torch = cuda
+    rng = np.random.default_rng(3)
+    batch, hq, hkv, seq, d = 2, 4, 2, 150, 128
+    big_q = torch.zeros((batch, hq, seq + 10, d + 64), device="cuda", dtype=torch.bfloat16)
+    big_o = torch.full((batch, hq, seq + 10, d + 64), 9.0, device="cuda", dtype=torch.bfloat16)
+    q = draw((batch, hq, seq, d), "bf16", rng)
+    k, v = (draw((batch, hkv, seq, d), "bf16", rng) for _ in range(2))
+    big_q[:, :, :seq, :d] = torch.from_numpy(q.view(np.int16)).cuda().view(torch.bfloat16)
+    dk, dv = (torch.from_numpy(x.view(np.int16)).cuda().view(torch.bfloat16) for x in (k, v))
+    calls.attention_forward(big_q[:, :, :seq, :d], dk, dv, big_o[:, :, :seq, :d], math.log2(math.e) / math.sqrt(d), True)
+    torch.cuda.synchronize()
+    assert bool((big_o[:, :, seq:] == 9).all()) and bool((big_o[..., d:] == 9).all())
+    got = o.bf16_values(big_o[:, :, :seq, :d].contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+    exact = o.attention_f64(o.bf16_values(q), o.bf16_values(k), o.bf16_values(v), True)
+    assert o.rel_frobenius(got, exact) < 1e-2
+
+
+def test_config_four_shape_statistics(cuda) -> None:
+    """The benchmark shape (B=8, Hq=32, Hkv=8, S=4096, D=128, causal, seed 3): a sample of (batch, head) pairs is
+    checked against float64, and every output row must be a convex combination of V rows (|o| <= max |v|)."""
+    torch = cuda
+    batch, hq, hkv, seq, d = 8, 32, 8, 4096, 128
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn((batch, hq, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
+    k = torch.randn((batch, hkv, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
+    v = torch.randn((batch, hkv, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    calls.attention_forward(q, k, v, out, math.log2(math.e) / math.sqrt(d), True)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(out.float()).all())
+    assert float(out.float().abs().max()) <= float(v.float().abs().max()) * 1.01
+    for b, h in ((0, 0), (3, 17), (7, 31)):
+        qs, ks, vs = q[b, h].double(), k[b, h // 4].double(), v[b, h // 4].double()
+        s = qs @ ks.t() / math.sqrt(d)
+        s = s.masked_fill(torch.ones(seq, seq, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+        exact = torch.softmax(s, dim=-1) @ vs
+        error = float((out[b, h].double() - exact).norm() / exact.norm())
+        assert error < 1e-2, (b, h, error)
+
+
+def test_refusals(cuda) -> None:
+    torch = cuda
+    q = torch.zeros((1, 2, 16, 96), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="head dimension 96 is not available on sm_100a"):
+        calls.attention_forward(q, q, q, q, 1.0, False)
+    q = torch.zeros((1, 3, 16, 64), device="cuda", dtype=torch.bfloat16)
+    k = torch.zeros((1, 2, 16, 64), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="bad extents"):
+        calls.attention_forward(q, k, k, q, 1.0, False)
