@@ -84,16 +84,18 @@ uint8_t krn_oracle_e4m3_encode(float x) {
   uint8_t sign = signbit(x) ? 0x80 : 0;
   float a = fabsf(x);
   if (a >= 448.0f) return sign | 0x7E;
-  /* codes 0..0x7E are monotone in value: binary search the bracketing pair, then pick nearest/even */
-  int lo = 0, hi = 0x7E;
-  while (hi - lo > 1) {
-    int mid = (lo + hi) / 2;
-    if (krn_oracle_e4m3_decode((uint8_t)mid) <= a) lo = mid; else hi = mid;
+  if (a < 0.015625f) {
+    /* below the smallest normal (2^-6): multiples of 2^-9, ties to even (nearbyintf in the default mode);
+     * a result of 8 is the code of 2^-6 itself */
+    return sign | (uint8_t)nearbyintf(a * 512.0f);
   }
-  float below = krn_oracle_e4m3_decode((uint8_t)lo), above = krn_oracle_e4m3_decode((uint8_t)hi);
-  float d_lo = a - below, d_hi = above - a;
-  int pick = d_lo < d_hi ? lo : (d_hi < d_lo ? hi : ((lo & 1) == 0 ? lo : hi));
-  return sign | (uint8_t)pick;
+  uint32_t bits;
+  memcpy(&bits, &a, 4);
+  bits += 0x7FFFFu + ((bits >> 20) & 1u); /* round the 23-bit mantissa to 3 bits, ties to even */
+  uint32_t exponent = (bits >> 23) - 127 + 7, mantissa = (bits >> 20) & 7u;
+  uint32_t code = (exponent << 3) | mantissa;
+  if (code > 0x7E) code = 0x7E; /* rounded past 448 */
+  return sign | (uint8_t)code;
 }
 
 void krn_oracle_e4m3_encode_array(const float* x, uint8_t* codes, int64_t count) {
