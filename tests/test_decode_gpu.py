@@ -71,5 +71,5 @@ def test_refusals_and_workspace(cuda) -> None:
     out = torch.empty_like(args[0])
     small = torch.empty(16, device="cuda", dtype=torch.uint8)
     with pytest.raises(Exception, match="KRN_B200_ERR_WORKSPACE"):
-        calls.attention_decode_fp8_paged(*args, out, 1.0, 128, small)
+        calls.attention_decode_fp8_paged(*args, out, 1.0, int(table.shape[1]) * 64, small)
     assert calls.decode_workspace_bytes(2, 4, 128, 128) == 2 * 4 * 1 * 130 * 4
