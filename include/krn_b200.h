@@ -109,6 +109,27 @@ int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages, const voi
                                    int64_t max_pages_per_seq, int64_t max_context, float scale_log2, void* workspace,
                                    int64_t workspace_bytes, void* stream);
 
+/* The same computation as krn_b200_attn_decode_fp8_paged, for callers that cannot allocate device memory when
+ * they need it — a serving loop whose KV-cache pool owns all remaining HBM, a plugin confined to another
+ * runtime's memory budget, a path where cudaMalloc's implicit synchronisation is not allowed. The split-KV
+ * partials go to a 16 MiB array built into the library image (each GPU that loads the library holds it until
+ * the process exits) instead of a caller workspace; the entry point calls no allocating routine at all.
+ *   limit    batch * q_heads * ceil(max_context / 1024) * 130 floats must fit 16 MiB (4 Mi floats); larger
+ *            problems are refused with KRN_B200_ERR_WORKSPACE — use the workspace variant for those.
+ *   set-up   the first call on each device resolves the array's device address (cudaGetSymbolAddress); make
+ *            that first call outside any stream capture.
+ *   sharing  every call on a device uses the same array, which keeps the previous call's partials. Nothing in
+ *            it has to start at zero (a call reads back only what it wrote), but two calls whose kernels overlap
+ *            on the GPU — different streams, or a graph replayed concurrently — race on it: serialise them.
+ *   status   a bounded device-side wait that expires is recorded in the status word only if an earlier call of
+ *            another entry point created that word on this device; this entry point does not create it.
+ * This entry point has no counterpart in the reference. */
+int krn_b200_attn_decode_fp8_paged_noalloc(const void* q, const void* k_pages, const void* v_pages,
+                                           const int32_t* page_table, const int32_t* context_len, const float* k_scale,
+                                           const float* v_scale, void* o, int64_t batch, int64_t q_heads,
+                                           int64_t kv_heads, int64_t d, int64_t page_size, int64_t max_pages_per_seq,
+                                           int64_t max_context, float scale_log2, void* stream);
+
 /* Copy this rank's column block C_local[M, n_local] into columns [col0, col0 + n_local) of the row-major
  * C_full[M, N] (ld in elements, elem_bytes 2 or 4). Used after the NCCL all-gather of GEMM output column
  * blocks to lay the gathered slabs out as one row-major matrix. No counterpart in the reference (it has no

@@ -26,6 +26,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <mutex>
 
 namespace krnb {
 namespace {
@@ -452,6 +453,128 @@ extern "C" int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages
   KRNB_CUDA(cudaGetLastError());
   decode_merge_kernel<<<dim3(unsigned(q_heads), unsigned(batch)), kD, 0, stream>>>(
       p.workspace, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads), p.chunks);
+  KRNB_CUDA(cudaGetLastError());
+  return KRN_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need attention: a serving loop
+// that has handed all free HBM to its KV-cache pool, a plugin running inside another runtime's memory budget,
+// or code on a path where an allocation (and the implicit synchronisation it can cause) is forbidden. For
+// them the split-KV partials live in a fixed array inside the library image instead of a caller workspace.
+// Every GPU that loads the library carries these 16 MiB until the process exits.
+namespace krnb {
+namespace {
+
+constexpr long long kStaticScratchFloats = 4ll * 1024 * 1024;  // 16 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+constexpr int kScratchDevices = 64;
+std::mutex g_scratch_mutex;
+float* g_scratch_address[kScratchDevices] = {nullptr};
+
+// Device address of g_decode_scratch on the CURRENT device. In host code the array's name is only a handle:
+// the address a kernel may dereference comes from cudaGetSymbolAddress, once per device, with that device
+// current.
+int static_scratch(float** address) {
+  int device = -1;
+  KRNB_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kScratchDevices) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "device ordinal %d is outside the supported range", device);
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    float* resolved = nullptr;
+    KRNB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&resolved), g_decode_scratch));
+    g_scratch_address[device] = resolved;
+  }
+  *address = g_scratch_address[device];
+  return KRN_B200_OK;
+}
+
+}  // namespace
+}  // namespace krnb
+
+extern "C" int krn_b200_attn_decode_fp8_paged_noalloc(const void* q, const void* k_pages, const void* v_pages,
+                                                      const int32_t* page_table, const int32_t* context_len,
+                                                      const float* k_scale, const float* v_scale, void* o,
+                                                      int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t d,
+                                                      int64_t page_size, int64_t max_pages_per_seq,
+                                                      int64_t max_context, float scale_log2, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (d != kD || page_size != kPage) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "paged decode with d = %lld, page size %lld is not available on sm_100a: "
+                "the kernel is built for 128-byte rows and 64-token pages. Instead: use d = 128 and page_size = 64",
+                (long long)d, (long long)page_size);
+  }
+  if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > kGroupMax) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "q_heads / kv_heads must be an integer of at most %d (got %lld / %lld)",
+                kGroupMax, (long long)q_heads, (long long)kv_heads);
+  }
+  if (batch == 0) return KRN_B200_OK;
+  if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr || context_len == nullptr ||
+      k_scale == nullptr || v_scale == nullptr || o == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  if (max_context <= 0 || max_pages_per_seq * kPage < max_context) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "max_context %lld does not fit %lld pages per sequence",
+                (long long)max_context, (long long)max_pages_per_seq);
+  }
+  const long long chunks = (max_context + kChunkTokens - 1) / kChunkTokens;
+  const long long need = (long long)batch * q_heads * chunks * (kD + 2);
+  if (need > kStaticScratchFloats) {
+    return fail(KRN_B200_ERR_WORKSPACE,
+                "batch %lld x q_heads %lld x %lld context chunks needs %lld scratch floats; the built-in scratch holds "
+                "%lld (16 MiB). Use krn_b200_attn_decode_fp8_paged with a caller workspace for larger problems",
+                (long long)batch, (long long)q_heads, chunks, need, kStaticScratchFloats);
+  }
+  if (!aligned16(k_pages) || !aligned16(v_pages)) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "page pools must be 16-byte aligned");
+  }
+  int major = 0;
+  {
+    int device = -1;
+    KRNB_CUDA(cudaGetDevice(&device));
+    KRNB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  }
+  if (major != 10) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "tcgen05 kernels is not available on this device: this library holds "
+                "sm_100a code only. Instead: run on a B200 (compute capability 10.x)");
+  }
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  // the status word exists only if a regular entry point created it earlier; this call never allocates one
+  DeviceContext* ctx = existing_context();
+  DeviceStatus* status = ctx != nullptr ? ctx->status_dev : nullptr;
+
+  const int64_t pool_pages = int64_t(1) << 22;
+  CUtensorMap map_k, map_v;
+  if (int rc = encode_pages(&map_k, k_pages, pool_pages, kv_heads)) return rc;
+  if (int rc = encode_pages(&map_v, v_pages, pool_pages, kv_heads)) return rc;
+
+  DecodeParams p;
+  p.q = static_cast<const uint16_t*>(q);
+  p.page_table = page_table;
+  p.context_len = context_len;
+  p.k_scale = k_scale;
+  p.workspace = scratch;
+  p.batch = int(batch);
+  p.q_heads = int(q_heads);
+  p.kv_heads = int(kv_heads);
+  p.group = int(q_heads / kv_heads);
+  p.max_pages = int(max_pages_per_seq);
+  p.chunks = int(chunks);
+  p.scale_log2 = scale_log2;
+
+  KRNB_CUDA(cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  decode_partial_kernel<<<dim3(unsigned(p.chunks), unsigned(kv_heads), unsigned(batch)), kThreads, kSmemBytes, stream>>>(
+      map_k, map_v, p, status);
+  KRNB_CUDA(cudaGetLastError());
+  decode_merge_kernel<<<dim3(unsigned(q_heads), unsigned(batch)), kD, 0, stream>>>(
+      scratch, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads), p.chunks);
   KRNB_CUDA(cudaGetLastError());
   return KRN_B200_OK;
 }

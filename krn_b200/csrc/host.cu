@@ -85,6 +85,13 @@ DeviceContext* current_context() {
   return &g_contexts[device];
 }
 
+DeviceContext* existing_context() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return g_ready[device] ? &g_contexts[device] : nullptr;
+}
+
 int require_sm100(const DeviceContext* ctx) {
   if (ctx->cc_major != 10) {
     return fail(KRN_B200_ERR_UNSUPPORTED,

@@ -43,6 +43,9 @@ struct DeviceContext {
 // Returns nullptr and sets the thread's error text on failure.
 DeviceContext* current_context();
 
+// Context of the current device if an earlier call already created it, else nullptr. Never allocates.
+DeviceContext* existing_context();
+
 // Refuse anything that is not a compute-capability 10.x device.
 int require_sm100(const DeviceContext* ctx);
 

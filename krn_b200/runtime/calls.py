@@ -105,6 +105,21 @@ def attention_decode_fp8_paged(q: Any, k_pages: Any, v_pages: Any, page_table: A
     native.check(status, "paged FP8 decode attention")
 
 
+def attention_decode_fp8_paged_noalloc(q: Any, k_pages: Any, v_pages: Any, page_table: Any, context_len: Any,
+                                       k_scale: Any, v_scale: Any, o: Any, scale_log2: float, max_context: int,
+                                       stream: Any = None) -> None:
+    """Paged FP8 decode attention for callers that cannot allocate device memory (no workspace argument: the
+    partials go to a 16 MiB array inside the kernel library). Calls on one device must not overlap on the GPU;
+    make the first call on a device outside stream capture."""
+    batch, hq, d = q.shape
+    _, page_size, hkv, _ = k_pages.shape
+    status = native.library().krn_b200_attn_decode_fp8_paged_noalloc(
+        _pointer(q), _pointer(k_pages), _pointer(v_pages), _pointer(page_table), _pointer(context_len),
+        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, page_table.shape[1],
+        max_context, scale_log2, _stream(stream))
+    native.check(status, "paged FP8 decode attention (built-in scratch)")
+
+
 def scatter_columns(slabs: Any, c_full: Any, ranks: int, stream: Any = None) -> None:
     """slabs [ranks, M, n_local] -> c_full [M, ranks * n_local] (row-major)."""
     _, m, n_local = slabs.shape

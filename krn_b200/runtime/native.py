@@ -34,6 +34,8 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
     "krn_b200_attn_decode_fp8_paged": (
         _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32,
                _ptr, _i64, _ptr]),
+    "krn_b200_attn_decode_fp8_paged_noalloc": (
+        _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _ptr]),
     "krn_b200_scatter_columns": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
 }
 
