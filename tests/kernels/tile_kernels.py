@@ -1,0 +1,136 @@
+"""Kernel sources the front-end tests capture (capture reads source files, so kernels live in a module)."""
+
+from krn_b200 import Const, Matrix, T, Tensor, arange, bf16, block, f16, f32, kernel, pipelined, struct, where, zeros
+
+
+@struct
+class Tiling:
+    bm: Const[int] = 128
+    bn: Const[int] = 128
+    bk: Const[int] = 32
+
+
+@kernel
+def matmul_nt(t: Tiling, a: Matrix[bf16], b: Matrix[bf16], c: Matrix[bf16]) -> None:
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk):
+        acc += a[rows, ks] @ b[cols, ks].transpose()
+    c[rows, cols] = acc.to(bf16)
+
+
+@kernel
+def matmul_nt_f16_f32(a: Matrix[f16], b: Matrix[f16], c: Matrix[f32]) -> None:
+    rows, cols = block.tile(32, 64)
+    acc = zeros(f32, 32, 64)
+    for ks in range(0, a.shape[1], 16):
+        acc += a[rows, slice(ks, ks + 16)] @ b[cols, slice(ks, ks + 16)].transpose()
+    c[rows, cols] = acc
+
+
+@kernel
+def matmul_nn(t: Tiling, a: Matrix[f16], b: Matrix[f16], c: Matrix[f16]) -> None:
+    """The reference example's row-major-B form (examples/04_libraries/01_gemm_tiles.py:35-40)."""
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk):
+        acc += a[rows, ks] @ b[ks, cols]
+    c[rows, cols] = acc.to(f16)
+
+
+@struct
+class Heads:
+    bq: Const[int] = 16
+    bk: Const[int] = 16
+    d: Const[int] = 64
+    causal: Const[bool] = False
+
+
+@kernel
+def flash_attention(t: Heads, q: Tensor[T.f16, int, int, int], k: Tensor[T.f16, int, int, int],
+                    v: Tensor[T.f16, int, int, int], o: Tensor[T.f16, int, int, int], scale: T.f32) -> None:
+    """The reference's example kernel, statement for statement (examples/04_libraries/08_flash_attention.py:35-59)."""
+    rows, head = block.tile(t.bq), block.index().y
+    q_pos = arange(t.bq, 0, rank=2, start=block.index().x * t.bq)
+    m, total, acc = zeros(T.f32, t.bq, 1).sub(1.0e30), zeros(T.f32, t.bq, 1), zeros(T.f32, t.bq, t.d)
+    qt = q[head, rows, slice(0, t.d)]
+    for c in range(0, k.shape[1], t.bk):
+        s = (qt @ k[head, c : c + t.bk, slice(0, t.d)].transpose()).mul(scale)
+        if t.causal:
+            s = where(arange(t.bk, 1, rank=2, start=c) <= q_pos, s, -1.0e30)
+        m_new = m.maximum(s.max(keepdims=True))
+        p, corr = (s - m_new).exp2(), (m - m_new).exp2()
+        total *= corr
+        total += p.sum(keepdims=True)
+        acc *= corr
+        acc += p.to(T.f16) @ v[head, c : c + t.bk, slice(0, t.d)]
+        m = m_new
+    o[head, rows, slice(0, t.d)] = (acc / total).to(T.f16)
+
+
+@struct
+class Grouped:
+    bq: Const[int] = 128
+    bk: Const[int] = 128
+    d: Const[int] = 128
+    group: Const[int] = 4
+
+
+@kernel
+def grouped_causal_attention(t: Grouped, q: Tensor[T.bf16, int, int, int, int], k: Tensor[T.bf16, int, int, int, int],
+                             v: Tensor[T.bf16, int, int, int, int], o: Tensor[T.bf16, int, int, int, int],
+                             scale: T.f32) -> None:
+    """Batched, grouped-query, causal: batch on grid z, `head // group` selects the kv head."""
+    rows, head, batch = block.tile(t.bq), block.index().y, block.index().z
+    q_pos = arange(t.bq, 0, rank=2, start=block.index().x * t.bq)
+    m, total, acc = zeros(T.f32, t.bq, 1).sub(1.0e30), zeros(T.f32, t.bq, 1), zeros(T.f32, t.bq, t.d)
+    qt = q[batch, head, rows, slice(0, t.d)]
+    for c in range(0, k.shape[2], t.bk):
+        s = (qt @ k[batch, head // t.group, c : c + t.bk, slice(0, t.d)].transpose()).mul(scale)
+        s = where(arange(t.bk, 1, rank=2, start=c) <= q_pos, s, -1.0e30)
+        m_new = m.maximum(s.max(keepdims=True))
+        p, corr = (s - m_new).exp2(), (m - m_new).exp2()
+        total *= corr
+        total += p.sum(keepdims=True)
+        acc *= corr
+        acc += p.to(T.bf16) @ v[batch, head // t.group, c : c + t.bk, slice(0, t.d)]
+        m = m_new
+    o[batch, head, rows, slice(0, t.d)] = (acc / total).to(T.bf16)
+
+
+@kernel
+def row_scale(a: Matrix[f32], c: Matrix[f32]) -> None:
+    """Not a contraction: the B200 device has no kernel for it."""
+    rows, cols = block.tile(16, 16)
+    c[rows, cols] = a[rows, cols] * 2.0
+
+
+@kernel
+def conflicting_tiles(a: Matrix[f32], c: Matrix[f32]) -> None:
+    rows = block.tile(8)
+    wide = block.tile(16)
+    c[rows, slice(0, 4)] = a[rows, slice(0, 4)]
+    c[wide, slice(4, 8)] = a[wide, slice(4, 8)]
+
+
+@kernel
+def mismatched_extents(a: Matrix[f32], b: Matrix[f32], c: Matrix[f32], d: Matrix[f32]) -> None:
+    rows, cols = block.tile(8, 8)
+    c[rows, cols] = a[rows, cols]
+    d[rows, cols] = b[rows, cols]
+
+
+@kernel
+def data_dependent_branch(a: Matrix[f32], c: Matrix[f32]) -> None:
+    rows, cols = block.tile(8, 8)
+    if a.shape[0] > 4:
+        c[rows, cols] = a[rows, cols]
+
+
+@kernel
+def fp8_needs_direct_loads(a: Matrix[T.f8e4m3fn], b: Matrix[T.f8e4m3fn], c: Matrix[f32]) -> None:
+    rows, cols = block.tile(32, 32)
+    acc = zeros(f32, 32, 32)
+    for ks in pipelined(a.shape[1], 32):
+        acc += a[rows, ks] @ (b[cols, ks] + b[cols, ks]).transpose()
+    c[rows, cols] = acc

@@ -1,0 +1,125 @@
+"""Host logic of the kernel-language surface, without a GPU: capture of the tile subset, launch-geometry inference
+(src/krn/compiler/space.py semantics, tests/frontend/test_launch_inference.py cases), the pattern recogniser and
+the refusal conventions."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import krn_b200 as krn
+from krn_b200 import Blocks, CaptureError, LaunchError, TargetError, Tiles
+from krn_b200.compiler import ir
+from krn_b200.compiler.capture import capture
+from krn_b200.compiler.recognise import AttentionPlan, GemmPlan, recognise
+from krn_b200.compiler.space import geometry
+from tests.kernels import tile_kernels as K
+
+
+def test_public_surface_names() -> None:
+    """The names a tile-kernel file imports from krn (src/krn/__init__.py:15-242)."""
+    for name in ("kernel", "struct", "Const", "AUTO", "T", "Matrix", "Tensor", "Tile", "QMatrix", "Tiles", "Blocks",
+                 "Items", "block", "pipelined", "zeros", "where", "arange", "maximum", "host", "configure", "config",
+                 "hw", "targets", "formats", "errors", "bf16", "f8e4m3fn", "f32"):
+        assert hasattr(krn, name), name
+    assert krn.T.bf16 is krn.bf16 and krn.T.f32(2.5).value == 2.5
+    assert krn.Matrix[krn.bf16].rank == 2 and krn.Tensor[krn.T.f16, int, int, int].rank == 3
+    target = krn.targets.Target.of("sm_100a")
+    assert target.has(krn.targets.Feature.TENSOR_MEMORY) and target.mma_native(krn.f8e4m3fn)
+    assert krn.formats.FP8FN().block == (1, 128) and krn.formats.E4M3FN.max == 448.0
+
+
+@pytest.mark.parametrize("shape,tile,want", [((50, 38), (16, 16), Blocks(3, 4)), ((1, 1), (8, 16), Blocks(1, 1)),
+                                             ((9, 17), (8, 16), Blocks(2, 2)), ((2, 200), (1, 16), Blocks(13, 2))])
+def test_tiles_blocks(shape, tile, want) -> None:
+    """`Tiles(shape, tile).blocks`: ceiling division, last axis along x (src/krn/frontend/geometry.py:28-41)."""
+    assert Tiles(shape, tile).blocks == want
+
+
+def test_gemm_capture_ir_and_inferred_geometry() -> None:
+    captured = capture(K.matmul_nt.fn, K.Tiling(bm=64, bn=32, bk=16))
+    loop = captured.body[1]
+    assert isinstance(loop, ir.For) and loop.pipelined and loop.step == 16 and loop.stop == ir.Dim("a", 1)
+    step = loop.body[0]
+    assert isinstance(step, ir.Accumulate) and isinstance(step.rhs, ir.Transpose) and step.rhs.shape == (16, 32)
+    axes = {axis.grid: axis for axis in captured.space}
+    assert {g: a.tile for g, a in axes.items()} == {"y": 64, "x": 32}
+    assert axes["y"].extents == (ir.Dim("c", 0),) and axes["x"].extents == (ir.Dim("c", 1),)  # stored extents win
+    args = [K.Tiling(), np.zeros((50, 70)), np.zeros((38, 70)), np.zeros((50, 38))]
+    assert geometry(captured, args) == Tiles((50, 38), (64, 32)).blocks
+    args[3] = np.zeros((1, 1))
+    assert geometry(captured, args) == Blocks(1, 1)  # a launch always has one block at least
+
+
+def test_recognise_gemm_forms() -> None:
+    plan = recognise(capture(K.matmul_nt.fn, K.Tiling()))
+    assert plan == GemmPlan("a", "b", "c", krn.bf16, krn.bf16, (128, 128, 32))
+    plan = recognise(capture(K.matmul_nt_f16_f32.fn))
+    assert plan == GemmPlan("a", "b", "c", krn.f16, krn.f32, (32, 64, 16))
+    with pytest.raises(TargetError) as error:
+        recognise(capture(K.matmul_nn.fn, K.Tiling()))
+    text = str(error.value)
+    assert "is not available on sm_100a" in text and "Instead:" in text and "transpose()" in text
+    assert "tile_kernels.py" in text and "^" in text  # compiler-style location with a caret
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_recognise_flash_attention_example(causal) -> None:
+    captured = capture(K.flash_attention.fn, K.Heads(causal=causal, d=128))
+    plan = recognise(captured)
+    assert plan == AttentionPlan("q", "k", "v", "o", ("scale",), krn.T.f16, 128, causal, False, 1, (16, 16))
+    # rows come from x only; the head is a scalar index, so y needs launch= as in the example
+    assert [(a.grid, a.tile) for a in captured.space] == [("x", 16)]
+    shapes = [K.Heads(), *(np.zeros((2, 200, 128)) for _ in range(4)), 1.0]
+    assert geometry(captured, shapes) == Blocks(13)
+
+
+def test_recognise_grouped_batched_attention() -> None:
+    plan = recognise(capture(K.grouped_causal_attention.fn, K.Grouped()))
+    assert isinstance(plan, AttentionPlan) and plan.batched and plan.group == 4 and plan.causal and plan.d == 128
+
+
+def test_refusals_follow_the_reference_conventions() -> None:
+    with pytest.raises(TargetError) as error:
+        recognise(capture(K.row_scale.fn))
+    assert error.value.feature == "kernel `row_scale`" and error.value.target == "sm_100a"
+    assert "no code generator" in error.value.reason
+    with pytest.raises(CaptureError, match="capture-time constant"):
+        capture(K.data_dependent_branch.fn)
+    with pytest.raises(CaptureError, match="loaded directly"):
+        capture(K.fp8_needs_direct_loads.fn)
+    with pytest.raises(TypeError, match="brackets take a configuration"):
+        K.matmul_nt[Tiles((4, 4), (2, 2))]
+    with pytest.raises(RuntimeError, match="device function"):
+        krn.zeros(krn.f32, 4, 4)
+
+
+def test_launch_errors() -> None:
+    captured = capture(K.mismatched_extents.fn)
+    with pytest.raises(LaunchError) as error:
+        geometry(captured, [np.zeros((37, 8)), np.zeros((9, 8)), np.zeros((37, 8)), np.zeros((9, 8))])
+    assert "mismatched_extents" in str(error.value) and "launch=" in str(error.value) and "[9, 37]" in str(error.value)
+    assert geometry(captured, [np.zeros((9, 8))] * 4) == Blocks(1, 2)  # and recovers once the shapes agree
+    with pytest.raises(LaunchError, match="more than one size"):
+        geometry(capture(K.conflicting_tiles.fn), [np.zeros((16, 4)), np.zeros((16, 4))])
+
+
+def test_settings_and_no_cpu_fallback(monkeypatch) -> None:
+    from krn_b200.errors import SettingError
+    from krn_b200.runtime import settings
+
+    assert krn.config.run.target == "sm_100a"
+    with pytest.raises(SettingError, match="no CPU fallback"):
+        krn.configure("run.target", "avx512")
+    with krn.configure("run.graphs", False):
+        assert krn.config.run.graphs is False
+    assert krn.config.run.graphs is True
+    pinned = K.Tiling(bm=64)
+    with krn.configure(**{"run__config": {"matmul_nt": pinned}}):
+        assert settings.current_settings().configuration("matmul_nt", K.Tiling) is pinned
+    assert settings.current_settings().configuration("matmul_nt", K.Tiling) == K.Tiling()
+    import torch
+
+    if not torch.cuda.is_available():
+        with pytest.raises(TargetError, match="no CPU fallback"):
+            krn.host.Device.current()
