@@ -59,8 +59,10 @@ int krn_b200_device_status(int* code, int* site, unsigned int* block);
  * src/krn/compiler/cuda.py:133-193).
  *   ab_type  KRN_B200_BF16 or KRN_B200_F16 (both operands)
  *   c_type   KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32
- *   lda/ldb/ldc  row pitches in ELEMENTS; pitch * element size and every base address must be multiples
- *                of 16 bytes. K == 0 stores zeros (the reference stores the untouched zero accumulator).
+ *   lda/ldb/ldc  row pitches in ELEMENTS. When every base address and pitch * element size is a multiple of 16
+ *                bytes the tcgen05 kernel runs; otherwise (e.g. the reference's 50 x 38 x 70 example) a plain
+ *                tiled f32-fma kernel computes the same product, slowly. K == 0 stores zeros (the reference
+ *                stores the untouched zero accumulator).
  * Ragged M, N, K are handled like the reference's invalid lanes: out-of-range operand elements read as
  * zero, out-of-range outputs are not stored (src/krn/compiler/emit.py:957-974,763-774). */
 int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
@@ -83,7 +85,7 @@ int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa,
  * max / sum in f32, P rounded to the storage type before P·V, output (acc / l) rounded once.
  *   q, o : [batch, q_heads, seq_q, d]    k, v : [batch, kv_heads, seq_kv, d]   (bf16, d contiguous)
  *   q_heads % kv_heads == 0 (grouped-query attention: q head h reads kv head h / (q_heads / kv_heads))
- *   causal != 0: key position j is visible to query position i when j <= i + (seq_kv - seq_q)
+ *   causal != 0: key position j is visible to query position i when j <= i (`kpos <= qpos`, as the example masks)
  *   *_stride_b / *_stride_h / *_stride_s: element strides of batch, head and sequence axes.
  * d must be 64 or 128. */
 int krn_b200_attn_fwd(int type, const void* q, const void* k, const void* v, void* o, int64_t batch, int64_t q_heads,

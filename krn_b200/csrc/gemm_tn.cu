@@ -20,6 +20,8 @@
 // elements arrive as zeros, out-of-range output elements are clipped.
 #include "gemm_common.cuh"
 
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 
 namespace krnb {
@@ -313,6 +315,54 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   return KRN_B200_OK;
 }
 
+// Operands whose addresses or row pitches are not multiples of 16 bytes cannot be described to TMA. They take this
+// plain tiled kernel instead (64 x 64 outputs per block, 16 of K per step, f32 fma in k order — the same chain the
+// reference's scalar fallback runs, src/krn/compiler/emit.py:806-821). It exists so odd shapes such as the
+// reference's 50 x 38 x 70 example still run on the device; it is not a performance path.
+__device__ __forceinline__ float load_16bit(const uint16_t* p, bool bf16) {
+  const uint16_t w = *p;
+  if (bf16) return __uint_as_float(uint32_t(w) << 16);
+  return __half2float(__ushort_as_half(w));
+}
+
+__global__ void __launch_bounds__(256)
+gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, void* __restrict__ c, int m,
+                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type) {
+  __shared__ float as[16][65], bs[16][65];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < k; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, kk = i & 15;
+      as[kk][r] = (row0 + r < m && k0 + kk < k) ? load_16bit(a + (long long)(row0 + r) * lda + k0 + kk, in_bf16) : 0.f;
+      bs[kk][r] = (col0 + r < n && k0 + kk < k) ? load_16bit(b + (long long)(col0 + r) * ldb + k0 + kk, in_bf16) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(as[kk][ty * 4 + i], bs[kk][tx * 4 + j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j) {
+      const int r = row0 + ty * 4 + i, col = col0 + tx * 4 + j;
+      if (r >= m || col >= n) continue;
+      const long long at = (long long)r * ldc + col;
+      if (c_type == KRN_B200_F32) {
+        static_cast<float*>(c)[at] = acc[i][j];
+      } else if (c_type == KRN_B200_BF16) {
+        static_cast<uint16_t*>(c)[at] = uint16_t(pack_bf16x2(acc[i][j], 0.f) & 0xffffu);
+      } else {
+        static_cast<uint16_t*>(c)[at] = uint16_t(pack_f16x2(acc[i][j], 0.f) & 0xffffu);
+      }
+    }
+}
+
 __global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitch_bytes, long long rows) {
   const long long total = rows * row_bytes;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -375,9 +425,17 @@ extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const vo
   }
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 ||
       (ldc * c_bytes) % 16 != 0) {
-    return fail(KRN_B200_ERR_INVALID_ARGUMENT,
-                "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld, ldc %lld elements)",
-                (long long)lda, (long long)ldb, (long long)ldc);
+    // not describable to TMA: the plain tiled kernel (element-aligned addresses are all it needs)
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 2 != 0 ||
+        reinterpret_cast<uintptr_t>(c) % c_bytes != 0) {
+      return fail(KRN_B200_ERR_INVALID_ARGUMENT, "tensor addresses must be aligned to their element size");
+    }
+    const dim3 grid(unsigned((n + 63) / 64), unsigned((m + 63) / 64), 1);
+    gemm_tn_unaligned_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b),
+                                                       c, int(m), int(n), int(k), lda, ldb, ldc,
+                                                       ab_type == KRN_B200_BF16, c_type);
+    KRNB_CUDA(cudaGetLastError());
+    return KRN_B200_OK;
   }
 
   const int group = gemm_pair_mode(m);
