@@ -4,23 +4,24 @@
 
 Default workload (N = 1): the bf16 tile product C = A @ B^T with M = N = K = 8192, f32 accumulation, bf16
 output — the configuration the headline metric is quoted on. A "step" is one pass of the hot path over one
-batch of synthetic operands (seeded N(0,1) rounded to bf16). Other workloads (`gemm_fp8`, `attn_fwd`,
-`attn_decode`) measure the other configurations with the same harness.
+batch of synthetic operands (seeded N(0,1)). The other workloads measure the other configurations with the same
+harness: `gemm_fp8` (block-scaled e4m3, 8192 x 28672 x 8192), `attn_fwd` (causal GQA flash attention, B=8, Hq=32,
+Hkv=8, S=4096, D=128), `attn_decode` (paged FP8 decode, 64 sequences, contexts 1024..8192).
 
 Keys of the line:
-  value       whole-job TFLOP/s with operands resident in HBM (CUDA events on the launching stream, max over ranks)
-  e2e         the same metric through the C-ABI call with HOST buffers: every step copies the operands from pinned
-              host memory, runs the kernel and reads the result back, all inside the timed region
-  roofline    achieved vs measured peak for the dominant kernel (algorithmic FLOPs / event time)
+  value         whole-job throughput with operands resident in HBM (CUDA events on the launching stream, max over ranks)
+  e2e           the same metric through the C-ABI call with HOST buffers: every step copies the operands from pinned
+                host memory, runs the kernel and reads the result back, all inside the timed region
+  roofline      achieved vs measured peak for the dominant kernel (algorithmic FLOPs or bytes / event time)
   cpu_baseline  the CPU restatement of the reference's C backend timed on this machine's cores on a bounded sample
-  clocks      SM clock and throttle reasons sampled by nvidia-smi during the timed region
+  clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region
 
-With N > 1 (launched by torch.distributed.run, one rank per GPU) the product is sharded by output column blocks:
-rank r multiplies A by its rows of B, the column blocks are all-gathered over NCCL and laid out as one row-major
-C on every rank; total work is fixed, so scaling is "strong".
+With N > 1 (launched by torch.distributed.run, one rank per GPU) total work is fixed ("strong" scaling): the tile
+products are sharded by output column blocks, all-gathered over NCCL and laid out as one row-major C on every rank;
+attention is sharded by (batch, kv head) and decode by sequence, with no collective.
 
 `--impl reference` times the reference's CPU implementation of the path (its C backend restated in oracle/, since
-the reference itself needs Python 3.14 + clang) on the host cores, rank 0 only.
+the reference itself needs Python 3.14 + clang and holds no C sources) on the host cores, rank 0 only.
 """
 
 from __future__ import annotations
@@ -39,10 +40,8 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-METRIC = "bf16_tile_gemm_tflops"
-
-# DRAM bytes per launch of the dominant kernel from the committed ncu capture (profiles/), or None when no
-# capture of that workload exists yet.
+# DRAM bytes per launch of the dominant kernel from the committed ncu captures (profiles/), None where no capture of
+# that workload exists yet.
 NCU_TRAFFIC_BYTES = {"gemm_bf16": None, "gemm_fp8": None, "attn_fwd": None, "attn_decode": None}
 
 
@@ -97,66 +96,85 @@ class ClockSampler:
 # ---- workloads --------------------------------------------------------------------------------------------------
 
 
-class GemmBf16:
-    """C = A @ B^T, bf16, M = N = K = 8192 (seed 1). Sharded by output column blocks across ranks."""
-
-    name, dtype, unit, bound = "gemm_bf16", "bf16", "TFLOP/s", "tensor"
-    description = "bf16 tile GEMM C=A@B^T M=N=K=8192, f32 accumulate, bf16 out (seed 1, N(0,1))"
-    m = n = k = 8192
+class Workload:
+    name = metric = dtype = description = ""
+    unit, bound = "TFLOP/s", "tensor"
+    launches_per_step = 1
 
     def __init__(self, torch, rank: int, world: int, size: list[int] | None = None) -> None:
         self.torch, self.rank, self.world = torch, rank, world
+
+    def scale(self, work: float, ms: float) -> float:
+        return work / (ms * 1e-3) / 1e12  # flop -> TFLOP/s (bytes -> GB/s overridden below)
+
+    def peak(self, peaks: dict) -> tuple[float, str]:
+        return peaks["bf16_tflops"], "burst (cuBLAS bf16 8192^3)"
+
+
+class GemmBf16(Workload):
+    """C = A @ B^T, bf16, M = N = K = 8192 (seed 1). Sharded by output column blocks across ranks."""
+
+    name, metric, dtype = "gemm_bf16", "bf16_tile_gemm_tflops", "bf16"
+    description = "bf16 tile GEMM C=A@B^T M=N=K=8192, f32 accumulate, bf16 out (seed 1, N(0,1))"
+    m = n = k = 8192
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        super().__init__(torch, rank, world)
+        from krn_b200 import sharding
+
         if size:
             self.m, self.n, self.k = size
             self.description = f"bf16 tile GEMM C=A@B^T M={self.m} N={self.n} K={self.k} (profiling case)"
-        self.n_local = self.n // world
+        begin, end = sharding.column_block(self.n, rank, world, 256) if world > 1 else (0, self.n)
+        self.n_local = end - begin
         gen = torch.Generator(device="cuda").manual_seed(1)
         self.a = torch.randn((self.m, self.k), device="cuda", generator=gen).to(torch.bfloat16)
         b = torch.randn((self.n, self.k), device="cuda", generator=gen).to(torch.bfloat16)
-        self.b = b[rank * self.n_local:(rank + 1) * self.n_local].contiguous()
+        self.b = b[begin:end].contiguous()
         del b
         self.c_local = torch.empty((self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
         if world > 1:
             self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
             self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
-        self.launches_per_step = 1 if world == 1 else 2
+            self.launches_per_step = 2
 
-    config = property(lambda self: {
-        "workload": self.description,
-        "m": self.m, "n": self.n, "k": self.k, "sharding": f"N-column blocks x{self.world}",
-        "l2": "operands and output (384 MiB) exceed the 126 MB L2; no flush between steps"})
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
+                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns",
+                "l2": "operands and output (384 MiB) exceed the 126 MB L2; no flush between steps"}
 
-    def flops(self) -> float:
+    def work(self) -> float:
         return 2.0 * self.m * self.n * self.k
 
-    def kernel_flops(self) -> float:
+    def kernel_work(self) -> float:
         return 2.0 * self.m * self.n_local * self.k
 
     def step(self, calls) -> None:
         stream = self.torch.cuda.current_stream()
         calls.gemm_tn(self.a, self.b, self.c_local, stream)
         if self.world > 1:
-            self.torch.distributed.all_gather_into_tensor(self.slabs, self.c_local)
-            calls.scatter_columns(self.slabs, self.c, self.world, stream)
+            from krn_b200 import sharding
+
+            sharding.gather_columns(self.c_local, self.slabs, self.c, self.world, stream=stream)
 
     def kernel_only(self, calls) -> None:
         calls.gemm_tn(self.a, self.b, self.c_local, self.torch.cuda.current_stream())
 
     def host_buffers(self):
-        torch = self.torch
         self.host_in = [t.cpu().pin_memory() for t in (self.a, self.b)]
-        self.host_out = torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
+        self.host_out = self.torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
         return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
         self.a.copy_(self.host_in[0], non_blocking=True)
         self.b.copy_(self.host_in[1], non_blocking=True)
-        calls.gemm_tn(self.a, self.b, self.c_local, self.torch.cuda.current_stream())
+        self.step(calls)
         self.host_out.copy_(self.c_local, non_blocking=True)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         """The faithful block loop (128x128x32 tiles) on the first `cores` block rows of the same problem, one
-        block row per thread; `columns` restricts N to bound the time. Returns (flops, description, callable)."""
+        block row per thread; `columns` restricts N to bound the time. Returns (work, description, callable)."""
         n = columns or self.n
         rows = 128 * cores
         a, b = oracle.config_gemm_bf16(rows, n, self.k, seed=1)
@@ -164,10 +182,254 @@ class GemmBf16:
         def run() -> None:
             oracle.gemm(a, b, ab_type=oracle.BF16, c_type=oracle.BF16, tile=(128, 128, 32), threads=cores)
 
-        return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the 8192^3 product, K=8192, {cores} threads", run
+        return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
 
 
-WORKLOADS = {"gemm_bf16": GemmBf16}
+class GemmFp8(Workload):
+    """Block-scaled e4m3 product, M=8192 N=28672 K=8192 (seed 2), 1x128 A scales, 128x128 B scales, bf16 out."""
+
+    name, metric, dtype = "gemm_fp8", "fp8_blockscaled_gemm_tflops", "fp8_e4m3"
+    description = "FP8 e4m3 block-scaled GEMM M=8192 N=28672 K=8192, fp32 scales 1x128 (A) / 128x128 (B), bf16 out (seed 2)"
+    m, n, k = 8192, 28672, 8192
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        super().__init__(torch, rank, world)
+        from krn_b200 import sharding
+
+        if size:
+            self.m, self.n, self.k = size
+            self.description = f"FP8 block-scaled GEMM M={self.m} N={self.n} K={self.k} (profiling case)"
+        begin, end = sharding.column_block(self.n, rank, world, 256) if world > 1 else (0, self.n)
+        self.n_local = end - begin
+        gen = torch.Generator(device="cuda").manual_seed(2)
+        self.a, self.sa = self._quantize(torch.randn((self.m, self.k), device="cuda", generator=gen), 1)
+        b = torch.randn((self.n, self.k), device="cuda", generator=gen)[begin:end].contiguous()
+        self.b, self.sb = self._quantize(b, 128)
+        del b
+        self.c_local = torch.empty((self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+        if world > 1:
+            self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+            self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+            self.launches_per_step = 2
+
+    def _quantize(self, x, block_rows: int):
+        """Codes with each block's absmax mapped to 448 (scale = absmax / 448), blocks of block_rows x 128."""
+        torch = self.torch
+        rows, cols = x.shape
+        blocks = x.view(rows // block_rows, block_rows, cols // 128, 128)
+        absmax = blocks.abs().amax(dim=(1, 3))
+        scale = torch.where(absmax > 0, absmax / 448.0, torch.ones_like(absmax))
+        codes = (blocks / scale[:, None, :, None]).reshape(rows, cols).to(torch.float8_e4m3fn)
+        return codes, scale.contiguous()
+
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
+                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns",
+                "l2": "operands and output (736 MiB) exceed the 126 MB L2; no flush between steps"}
+
+    def work(self) -> float:
+        return 2.0 * self.m * self.n * self.k
+
+    def kernel_work(self) -> float:
+        return 2.0 * self.m * self.n_local * self.k
+
+    def peak(self, peaks: dict) -> tuple[float, str]:
+        return 2.0 * peaks["bf16_tflops"], "2 x burst cuBLAS bf16 (no FP8 peak was measured on this pool)"
+
+    def step(self, calls) -> None:
+        stream = self.torch.cuda.current_stream()
+        calls.gemm_fp8_blockscaled_tn(self.a, self.sa, self.b, self.sb, self.c_local, stream)
+        if self.world > 1:
+            from krn_b200 import sharding
+
+            sharding.gather_columns(self.c_local, self.slabs, self.c, self.world, stream=stream)
+
+    def kernel_only(self, calls) -> None:
+        calls.gemm_fp8_blockscaled_tn(self.a, self.sa, self.b, self.sb, self.c_local, self.torch.cuda.current_stream())
+
+    def host_buffers(self):
+        torch = self.torch
+        self.device_in = [t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in (self.a, self.sa, self.b, self.sb)]
+        self.host_in = [t.cpu().pin_memory() for t in self.device_in]
+        self.host_out = torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
+        return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
+
+    def e2e_step(self, calls) -> None:
+        for dst, src in zip(self.device_in, self.host_in):
+            dst.copy_(src, non_blocking=True)
+        self.step(calls)
+        self.host_out.copy_(self.c_local, non_blocking=True)
+
+    def cpu_sample(self, oracle, cores: int, columns: int | None = None):
+        n = columns or 2048
+        rows = 64 * cores
+        a_codes, sa, b_codes, sb = oracle.config_gemm_fp8(rows, n, self.k, seed=2)
+
+        def run() -> None:
+            oracle.gemm_fp8_blockscaled(a_codes, sa, b_codes, sb, threads=cores)
+
+        return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
+
+
+class AttnFwd(Workload):
+    """Causal GQA flash attention forward, B=8 Hq=32 Hkv=8 S=4096 D=128, bf16 (seed 3). Sharded by batch."""
+
+    name, metric, dtype = "attn_fwd", "flash_attn_fwd_tflops", "bf16"
+    description = "bf16 causal flash-attention forward B=8 Hq=32 Hkv=8 S=4096 D=128 (seed 3, N(0,1))"
+    batch, hq, hkv, seq, d = 8, 32, 8, 4096, 128
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        super().__init__(torch, rank, world)
+        from krn_b200 import sharding
+
+        if size:
+            self.batch, self.hq, self.hkv, self.seq, self.d = size
+            self.description = f"causal flash attention B={self.batch} Hq={self.hq} Hkv={self.hkv} S={self.seq} D={self.d}"
+        units = sharding.contiguous_units(self.batch, rank, world)  # whole batches = contiguous (batch, kv head) units
+        self.batch_local = len(units)
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        shape_q, shape_kv = (self.batch, self.hq, self.seq, self.d), (self.batch, self.hkv, self.seq, self.d)
+        q, k, v = (torch.randn(s, device="cuda", generator=gen).to(torch.bfloat16) for s in (shape_q, shape_kv, shape_kv))
+        self.q, self.k, self.v = (t[units.start:units.stop].contiguous() for t in (q, k, v))
+        del q, k, v
+        self.o = torch.empty_like(self.q)
+        self.scale_log2 = math.log2(math.e) / math.sqrt(self.d)
+
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "sharding": f"(batch, kv head) units x{self.world}, no collective",
+                "l2": "Q, K, V, O (640 MiB) exceed the 126 MB L2; no flush between steps"}
+
+    def work(self) -> float:
+        return 4.0 * self.batch * self.hq * self.d * self.seq * (self.seq + 1) / 2
+
+    def kernel_work(self) -> float:
+        return self.work() * self.batch_local / self.batch
+
+    def step(self, calls) -> None:
+        if self.batch_local:
+            calls.attention_forward(self.q, self.k, self.v, self.o, self.scale_log2, True, self.torch.cuda.current_stream())
+
+    kernel_only = step
+
+    def host_buffers(self):
+        self.host_in = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
+        self.host_out = self.torch.empty(self.o.shape, dtype=self.o.dtype).pin_memory()
+        return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
+
+    def e2e_step(self, calls) -> None:
+        for dst, src in zip((self.q, self.k, self.v), self.host_in):
+            dst.copy_(src, non_blocking=True)
+        self.step(calls)
+        self.host_out.copy_(self.o, non_blocking=True)
+
+    def cpu_sample(self, oracle, cores: int, columns: int | None = None):
+        heads = cores
+        seq = columns or 2048
+        q, k, v = oracle.config_attention(1, heads, max(1, heads // 4), seq, self.d, seed=3)
+
+        def run() -> None:
+            oracle.flash_attention(q, k, v, dtype=oracle.BF16, scale=self.scale_log2, causal=True, bq=64, bk=64, threads=cores)
+
+        return (4.0 * heads * self.d * seq * (seq + 1) / 2,
+                f"{heads} q heads of one batch at S={seq} (causal, 64x64 tiles), {cores} threads", run)
+
+
+class AttnDecode(Workload):
+    """Paged FP8 decode attention, 64 sequences with contexts U[1024, 8192] (seed 4). HBM-bound: GB/s."""
+
+    name, metric, dtype = "attn_decode", "paged_fp8_decode_gbs", "fp8_e4m3"
+    unit, bound = "GB/s", "hbm"
+    description = "FP8 e4m3 paged decode attention B=64 Hq=32 Hkv=8 D=128, contexts U[1024,8192], page 64 (seed 4)"
+    batch, hq, hkv, d, page = 64, 32, 8, 128, 64
+    launches_per_step = 2
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        super().__init__(torch, rank, world)
+        import numpy as np
+
+        from krn_b200 import sharding
+        from krn_b200.runtime import calls
+
+        rng = np.random.default_rng(4)
+        lens = rng.integers(1024, 8193, self.batch).astype(np.int32)
+        mine = sharding.balanced_by_length(lens, world)[rank]
+        self.all_tokens = int(lens.sum())
+        lens = lens[mine]
+        self.local = len(mine)
+        self.tokens = int(lens.sum())
+        pages = -(-lens // self.page)
+        self.max_pages = 8192 // self.page
+        pool = int(pages.sum())
+        order = rng.permutation(pool).astype(np.int32)
+        table = np.zeros((self.local, self.max_pages), np.int32)
+        cursor = 0
+        for i, count in enumerate(pages):
+            table[i, :count] = order[cursor:cursor + count]
+            cursor += int(count)
+        gen = torch.Generator(device="cuda").manual_seed(4 + rank)
+        shape = (pool, self.page, self.hkv, self.d)
+        self.k_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).to(torch.float8_e4m3fn)
+        self.v_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).to(torch.float8_e4m3fn)
+        self.k_scale = torch.rand((self.local, self.hkv), device="cuda", generator=gen) * 0.01 + 0.005
+        self.v_scale = torch.rand((self.local, self.hkv), device="cuda", generator=gen) * 0.01 + 0.005
+        self.q = torch.randn((self.local, self.hq, self.d), device="cuda", generator=gen).to(torch.bfloat16)
+        self.table, self.lens = torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda()
+        self.o = torch.empty_like(self.q)
+        self.scale_log2 = math.log2(math.e) / math.sqrt(self.d)
+        self.workspace = torch.empty(calls.decode_workspace_bytes(self.local, self.hq, self.d, 8192), device="cuda",
+                                     dtype=torch.uint8)
+
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "sharding": f"sequences balanced by length x{self.world}, no collective",
+                "l2": "the cache pages read per step (~0.6 GB) exceed the 126 MB L2; no flush between steps"}
+
+    def _bytes(self, tokens: int, sequences: int) -> float:
+        return tokens * 2.0 * self.hkv * self.d + 2.0 * sequences * self.hq * self.d * 2 + 4.0 * tokens / self.page
+
+    def work(self) -> float:
+        return self._bytes(self.all_tokens, self.batch)
+
+    def kernel_work(self) -> float:
+        return self._bytes(self.tokens, self.local)
+
+    def scale(self, work: float, ms: float) -> float:
+        return work / (ms * 1e-3) / 1e9  # GB/s
+
+    def peak(self, peaks: dict) -> tuple[float, str]:
+        return peaks["hbm_gbs"], "STREAM-style copy bandwidth"
+
+    def step(self, calls) -> None:
+        calls.attention_decode_fp8_paged(self.q, self.k_pages, self.v_pages, self.table, self.lens, self.k_scale,
+                                         self.v_scale, self.o, self.scale_log2, 8192, self.workspace,
+                                         self.torch.cuda.current_stream())
+
+    kernel_only = step
+
+    def host_buffers(self):
+        # the cache lives on the device in a decode loop; per step the host sends the query and reads the output
+        self.host_in = [self.q.cpu().pin_memory()]
+        self.host_out = self.torch.empty(self.o.shape, dtype=self.o.dtype).pin_memory()
+        return self.host_in[0].numel() * 2, self.host_out.numel() * 2
+
+    def e2e_step(self, calls) -> None:
+        self.q.copy_(self.host_in[0], non_blocking=True)
+        self.step(calls)
+        self.host_out.copy_(self.o, non_blocking=True)
+
+    def cpu_sample(self, oracle, cores: int, columns: int | None = None):
+        config = oracle.config_decode(batch=cores, q_heads=self.hq, kv_heads=self.hkv, d=self.d, low=1024, high=2048, seed=4)
+        tokens = int(config[4].sum())
+
+        def run() -> None:
+            oracle.decode_fp8_paged(*config, scale_log2=self.scale_log2, threads=cores)
+
+        return self._bytes(tokens, cores), f"{cores} sequences with contexts U[1024,2048], {cores} threads", run
+
+
+WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, AttnFwd, AttnDecode)}
 
 
 def reference_arm(args, rank: int) -> int:
@@ -177,21 +439,23 @@ def reference_arm(args, rank: int) -> int:
     from oracle import oracle
 
     cores = min(os.cpu_count() or 1, 64)
-    workload = WORKLOADS[args.workload].__new__(WORKLOADS[args.workload])
-    workload.world = 1
-    flops, sample, run = workload.cpu_sample(oracle, cores, columns=1024)
-    for _ in range(min(args.warmup, 1)):
+    kind = WORKLOADS[args.workload]
+    workload = kind.__new__(kind)
+    workload.world, workload.scale_log2 = 1, math.log2(math.e) / math.sqrt(128)
+    work, sample, run = workload.cpu_sample(oracle, cores, columns=1024)
+    warmup = min(args.warmup, 1)
+    for _ in range(warmup):
         run()
     start = time.perf_counter()
     for _ in range(args.steps):
         run()
     seconds = time.perf_counter() - start
-    value = flops * args.steps / seconds / 1e12
+    value = workload.scale(work * args.steps, seconds * 1e3)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": workload.unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": seconds / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": workload.dtype,
-        "data": "synthetic", "config": {"workload": workload.description},
+        "impl": "reference", "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic",
+        "config": {"workload": workload.description},
         "cpu_baseline": {"value": value, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -264,15 +528,17 @@ def main() -> int:
     clocks = sampler.summary()
     native.raise_device_status()
     ms_per_step = total_ms / args.steps
-    value = workload.flops() / (ms_per_step * 1e-3) / 1e12
+    value = workload.scale(workload.work(), ms_per_step)
 
     # ---- the dominant kernel alone (roofline) ---------------------------------------------------------------------
     kernel_ms = timed(lambda: workload.kernel_only(calls), args.steps) / args.steps
-    achieved = workload.kernel_flops() / (kernel_ms * 1e-3) / 1e12
-    peak = peaks["bf16_tflops"]
-    roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES[workload.name], "peak_kind": f"{peak_kind} burst (cuBLAS bf16 8192^3)",
-                "kernel_ms": kernel_ms, "frac_of_nominal_dense_peak": achieved / 2250.0}
+    achieved = workload.scale(workload.kernel_work(), kernel_ms)
+    peak, peak_note = workload.peak(peaks)
+    roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit, "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES[workload.name], "peak_kind": f"{peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
+    if workload.bound == "tensor":
+        nominal = 4500.0 if workload.dtype.startswith("fp8") else 2250.0
+        roofline["frac_of_nominal_dense_peak"] = achieved / nominal
 
     # ---- end to end with host buffers ---------------------------------------------------------------------------------
     e2e = None
@@ -282,7 +548,7 @@ def main() -> int:
             workload.e2e_step(calls)
         e2e_steps = max(3, min(args.steps, 10))
         e2e_ms = timed(lambda: workload.e2e_step(calls), e2e_steps) / e2e_steps
-        e2e = {"value": workload.flops() / (e2e_ms * 1e-3) / 1e12, "unit": workload.unit,
+        e2e = {"value": workload.scale(workload.work(), e2e_ms), "unit": workload.unit,
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms}
         native.raise_device_status()
 
@@ -292,20 +558,20 @@ def main() -> int:
         from oracle import oracle
 
         cores = min(os.cpu_count() or 1, 64)
-        flops, sample, run = workload.cpu_sample(oracle, cores)
+        work, sample, run = workload.cpu_sample(oracle, cores)
         start = time.perf_counter()
         run()
         seconds = time.perf_counter() - start
-        cpu = {"value": flops / seconds / 1e12, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample,
-               "seconds": seconds}
+        cpu = {"value": workload.scale(work, seconds * 1e3), "unit": workload.unit, "cores": cores, "kind": "port",
+               "sample": sample, "seconds": seconds}
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": workload.dtype, "data": "synthetic", "config": workload.config, "roofline": roofline,
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": workload.launches_per_step * args.steps, "clocks": clocks,
-            "frac_of_nominal_dense_peak": value / (2250.0 * world),
+            "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic", "config": workload.config,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": workload.launches_per_step * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if distributed:
