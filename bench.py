@@ -520,10 +520,11 @@ def main() -> int:
         workload.step(calls)
     with ClockSampler(local_rank) as sampler:
         total_ms = timed(lambda: workload.step(calls), args.steps)
-        # keep the GPU busy long enough for nvidia-smi to see it under load
+        # keep the GPU busy long enough for nvidia-smi to see it under load; the kernel alone, because the number of
+        # iterations differs between ranks and a step of N > 1 holds a collective
         deadline = time.time() + 0.6
         while time.time() < deadline and len(sampler.samples) < 3:
-            workload.step(calls)
+            workload.kernel_only(calls)
             torch.cuda.synchronize()
     clocks = sampler.summary()
     native.raise_device_status()
