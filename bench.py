@@ -42,7 +42,11 @@ if str(ROOT) not in sys.path:
 
 # DRAM bytes per launch of the dominant kernel from the committed ncu captures (profiles/), None where no capture of
 # that workload exists yet.
-NCU_TRAFFIC_BYTES = {"gemm_bf16": None, "gemm_fp8": None, "attn_fwd": None, "attn_decode": None}
+# gemm_bf16 / gemm_fp8 / attn_fwd: captured on a smaller case (see profiles/) and scaled to the full launch by the
+# algorithmic bytes, which DRAM traffic follows for these streaming operand/output patterns; attn_decode: captured on
+# the bench workload itself.
+NCU_TRAFFIC_BYTES = {"gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(340.0e6 * 773.9 / 193.5),
+                     "attn_fwd": int(137.6e6 * 671.1 / 167.8), "attn_decode": int(690.2e6)}
 
 
 def measured_peaks() -> tuple[dict, str]:
