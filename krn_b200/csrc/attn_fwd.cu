@@ -12,7 +12,8 @@
 //                 O_t += P_t V (A = P_t read FROM tensor memory, B = V as an MN-major shared-memory operand),
 //                 interleaved over the two query tiles so the tensor cores work on one tile while the other
 //                 tile's softmax runs;
-//   warps 4..7    softmax of query tile 0; warps 8..11 softmax of tile 1 (232 registers each via setmaxnreg). A thread owns one query row: it
+//   warps 4..7    softmax of query tile 0; warps 8..11 softmax of tile 1 (224 registers each via setmaxnreg; the
+//                 producer / MMA warpgroup keeps 56 so that the MMA issue loop does not spill). A thread owns one query row: it
 //                 reads its row of S from tensor memory, applies the mask, updates m and l, writes P (bf16)
 //                 back over S, and rescales its row of O in tensor memory when the maximum moved by more than
 //                 2^8 (below that the old reference maximum is kept, which leaves the quotient acc/l unchanged).
@@ -131,7 +132,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) reg_dealloc<40>();
+  if (warp < 4) reg_dealloc<56>();
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -228,7 +229,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax + epilogue warps
-    reg_alloc<232>();
+    reg_alloc<224>();
     const int t = (warp - 4) >> 2;   // query tile of this warpgroup
     const int quarter = warp & 3;    // tensor-memory lane quarter
     const int nt = t == 0 ? n0 : n1;
@@ -396,10 +397,10 @@ int launch(const DeviceContext* ctx, const CUtensorMap& mq, const CUtensorMap& m
            const CUtensorMap& mo, AttnParams p, cudaStream_t stream) {
   auto kernel = attn_fwd_kernel<D, BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<D>::kSmemBytes));
-  // setmaxnreg.inc blocks until the CTA's register pool can cover it: 128 x (R - 40) must reach 256 x (232 - R)
+  // setmaxnreg.inc blocks until the CTA's register pool can cover it: 128 x (R - 56) must reach 256 x (224 - R)
   cudaFuncAttributes attributes;
   KRNB_CUDA(cudaFuncGetAttributes(&attributes, kernel));
-  if ((attributes.numRegs - 40) * 128 < (232 - attributes.numRegs) * 256) {
+  if ((attributes.numRegs - 56) * 128 < (224 - attributes.numRegs) * 256) {
     return fail(KRN_B200_ERR_UNSUPPORTED, "attention kernel was built with %d registers per thread; the register "
                 "re-partitioning needs at least 168", attributes.numRegs);
   }
