@@ -136,16 +136,23 @@ class GemmBf16(Workload):
         b = torch.randn((self.n, self.k), device="cuda", generator=gen).to(torch.bfloat16)
         self.b = b[begin:end].contiguous()
         del b
+        self.columns = slice(begin, end)
         self.c_local = torch.empty((self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+        self.fused = None
         if world > 1:
-            self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
-            self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+            if os.environ.get("KRN_B200_GATHER", "fused") == "fused":
+                self.fused = sharding.GatheredProduct(self.m, self.n, torch.bfloat16)
+            else:
+                self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+                self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
             self.launches_per_step = 2
 
     @property
     def config(self) -> dict:
+        gather = ("all-gather of the output columns fused into the product kernel (TMA stores into every rank's C over "
+                  "NVLink) + device barrier" if self.fused else "NCCL all-gather of the output columns + re-layout kernel")
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
-                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns",
+                "sharding": f"N-column blocks x{self.world}, {gather}",
                 "l2": "operands and output (384 MiB) exceed the 126 MB L2; no flush between steps"}
 
     def work(self) -> float:
@@ -156,6 +163,9 @@ class GemmBf16(Workload):
 
     def step(self, calls) -> None:
         stream = self.torch.cuda.current_stream()
+        if self.fused is not None:
+            self.fused.run(self.a, self.b, stream)
+            return
         calls.gemm_tn(self.a, self.b, self.c_local, stream)
         if self.world > 1:
             from krn_b200 import sharding
@@ -174,7 +184,8 @@ class GemmBf16(Workload):
         self.a.copy_(self.host_in[0], non_blocking=True)
         self.b.copy_(self.host_in[1], non_blocking=True)
         self.step(calls)
-        self.host_out.copy_(self.c_local, non_blocking=True)
+        result = self.c_local if self.fused is None else self.fused.c[:, self.columns]
+        self.host_out.copy_(result, non_blocking=True)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         """The faithful block loop (128x128x32 tiles) on the first `cores` block rows of the same problem, one

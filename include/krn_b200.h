@@ -68,6 +68,20 @@ int krn_b200_device_status(int* code, int* site, unsigned int* block);
 int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
                      int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
+/* The same product sharded by output columns over the GPUs of one node, with the all-gather of the output
+ * columns done by the kernel itself: rank `rank` of `ranks` multiplies A[M,K] by ITS rows of B (b: [n_local, K])
+ * and its epilogue stores the column block [rank * n_local, (rank + 1) * n_local) into EVERY rank's C —
+ * c_of_rank[r] is the address, valid on this device, of rank r's full row-major C[M, ranks * n_local] (its own
+ * buffer for r == rank, NVLink peer mappings for the others, e.g. from torch symmetric memory). The stores are TMA
+ * stores issued tile by tile while the next tile is being multiplied; no load ever targets a peer and nothing is
+ * multicast. A cross-rank barrier after the call (all ranks finished their kernel) makes every C complete.
+ * n_local must be a multiple of 128 bytes of output (64 columns of bf16/f16, 32 of f32); all addresses and pitches
+ * 16-byte aligned. `c_of_rank` is a HOST array of `ranks` pointers (ranks <= 8). No counterpart in the reference,
+ * which has no multi-device path. */
+int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank, int ranks,
+                            int rank, int64_t m, int64_t n_local, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                            void* stream);
+
 /* C[M,N] = sum over 128-wide K blocks kb of  sa[m,kb] * sb[n/128,kb] * (A8[m, kb] . B8[n, kb]),
  * A8/B8 e4m3fn codes (one byte each, K-major), sa f32 [M, ceil(K/128)] (one scale per 1x128 block of A,
  * the reference's FP8FN block format, src/krn/data/formats.py:157-164), sb f32 [ceil(N/128), ceil(K/128)]

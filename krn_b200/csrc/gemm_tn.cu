@@ -45,12 +45,24 @@ struct Layout {
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
 };
 
+// Where the output goes. One map for a plain product. When the product is sharded by output columns over the GPUs
+// of a node, one map per rank: every rank's full C (its own and, through NVLink peer mappings, the others'),
+// and this rank's column block is stored into all of them at `column_offset` — the all-gather of the output
+// columns happens in the epilogue's TMA stores, tile by tile, while the main loop works on the next tile.
+// (TMA STORES to peer memory; no load ever targets a peer and nothing is multicast.)
+constexpr int kMaxDestinations = 8;
+struct Destinations {
+  CUtensorMap maps[kMaxDestinations];
+  int count;
+  int column_offset;
+};
+
 enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
 
 template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, Problem p, uint32_t ab_format, DeviceStatus* status) {
+               const __grid_constant__ Destinations dst, Problem p, uint32_t ab_format, DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kBK = kRowBytes / ELEM_BYTES;                 // K elements per stage
   constexpr int kChunkCols = kRowBytes / int(sizeof(OutT));   // output columns per 128-byte store row
@@ -93,7 +105,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
-    prefetch_tensormap(&map_c);
+    for (int d = 0; d < dst.count; ++d) prefetch_tensormap(&dst.maps[d]);
   }
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
@@ -253,7 +265,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_c, col, row0, buffer);
+            // one box, every destination: the own output and, when sharded, each peer's copy of C
+            for (int d = 0; d < dst.count; ++d) tma_store_2d(&dst.maps[d], col + dst.column_offset, row0, buffer);
             tma_store_commit();
           }
           ++stores;
@@ -291,7 +304,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
-int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
            uint32_t fmt, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_tn_kernel<CTA_GROUP, 2, OutT, OUT_BF16>;
@@ -387,6 +400,60 @@ int gemm_pair_mode(int64_t m) {
 
 }  // namespace krnb
 
+// Encode the operand and destination maps and launch the tile kernel: C_d[:, offset : offset + n] = A . B^T for every
+// destination d (each a row-major matrix of n_total columns with pitch ldc).
+static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type, const void* a, const void* b,
+                         void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m,
+                         int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream) {
+  using namespace krnb;
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  Problem p;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
+  p.tiles_n = int((n + kBN - 1) / kBN);
+
+  const CUtensorMapDataType ab_dt = ab_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(lda) * 2};
+    uint32_t box[2] = {64, uint32_t(kBM)};
+    if (int rc = encode_tensor_map(&map_a, ab_dt, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
+    uint64_t strides[1] = {uint64_t(ldb) * 2};
+    uint32_t box[2] = {64, uint32_t(kBN / group)};
+    if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  Destinations dst;
+  dst.count = count;
+  dst.column_offset = int(column_offset);
+  for (int d = 0; d < kMaxDestinations; ++d) {
+    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t dims[2] = {uint64_t(n_total), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    // unused slots repeat the first destination so that every map in the struct is a valid descriptor
+    void* base = destinations[d < count ? d : 0];
+    if (int rc = encode_tensor_map(&dst.maps[d], c_dt, 2, base, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  const uint32_t fmt = ab_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
+  if (group == 2) {
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, fmt, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+  }
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, fmt, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+}
+
 extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
   using namespace krnb;
@@ -439,44 +506,51 @@ extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const vo
   }
 
   const int group = gemm_pair_mode(m);
-  Problem p;
-  p.m = int(m);
-  p.n = int(n);
-  p.k = int(k);
-  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
-  p.tiles_n = int((n + kBN - 1) / kBN);
+  void* destinations[1] = {c};
+  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream);
+}
 
-  const CUtensorMapDataType ab_dt = ab_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUtensorMap map_a, map_b, map_c;
-  {
-    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
-    uint64_t strides[1] = {uint64_t(lda) * 2};
-    uint32_t box[2] = {64, uint32_t(kBM)};
-    if (int rc = encode_tensor_map(&map_a, ab_dt, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank,
+                                       int ranks, int rank, int64_t m, int64_t n_local, int64_t k, int64_t lda,
+                                       int64_t ldb, int64_t ldc, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "operand type %d is not available on sm_100a: this entry point multiplies "
+                "16-bit tiles. Instead: pass KRN_B200_BF16 or KRN_B200_F16", ab_type);
   }
-  {
-    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
-    uint64_t strides[1] = {uint64_t(ldb) * 2};
-    uint32_t box[2] = {64, uint32_t(kBN / group)};
-    if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
   }
-  {
-    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
-    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
-    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
-    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  if (ranks < 1 || ranks > kMaxDestinations || rank < 0 || rank >= ranks) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "rank %d of %d: between 1 and %d ranks are supported", rank, ranks,
+                kMaxDestinations);
   }
-  const uint32_t fmt = ab_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
-  if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, fmt, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  if (m <= 0 || n_local <= 0 || k <= 0 || m > INT32_MAX || n_local * ranks > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "extents must be positive and below 2^31 (m %lld, n_local %lld, k %lld)",
+                (long long)m, (long long)n_local, (long long)k);
   }
-  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, fmt, stream);
-  return launch<1, uint16_t, false>(ctx, map_a, map_b, map_c, p, fmt, stream);
+  if (n_local % (128 / c_bytes) != 0) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "a column block of %lld columns is not a whole number of 128-byte store "
+                "rows, so its last store would reach into the next rank's block. Instead: shard N in multiples of "
+                "%d columns", (long long)n_local, 128 / c_bytes);
+  }
+  if (a == nullptr || b == nullptr || c_of_rank == nullptr || lda < k || ldb < k || ldc < n_local * ranks) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address or row pitch shorter than the row");
+  }
+  bool aligned = aligned16(a) && aligned16(b) && (lda * 2) % 16 == 0 && (ldb * 2) % 16 == 0 && (ldc * c_bytes) % 16 == 0;
+  void* destinations[kMaxDestinations];
+  for (int r = 0; r < ranks; ++r) {
+    destinations[r] = c_of_rank[r];
+    aligned = aligned && c_of_rank[r] != nullptr && aligned16(c_of_rank[r]);
+  }
+  if (!aligned) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the sharded product needs 16-byte aligned addresses and row pitches");
+  }
+  DeviceContext* ctx = current_context();
+  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
+  if (int rc = require_sm100(ctx)) return rc;
+  return tiled_product(ctx, ab_type, c_type, a, b, destinations, ranks, rank * n_local, n_local * ranks, m, n_local, k, lda,
+                       ldb, ldc, gemm_pair_mode(m), stream);
 }

@@ -57,6 +57,21 @@ def gemm_tn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
     native.check(status, "tile matrix product")
 
 
+def gemm_tn_gather(a: Any, b_local: Any, c_pointers: list[int], rank: int, m: int, n_local: int, ldc: int, c_type: int,
+                   stream: Any = None) -> None:
+    """This rank's column block of c = a @ b^T, stored by the kernel's epilogue into every rank's full C.
+    `c_pointers[r]` is the address (valid on this device) of rank r's row-major C[m, len(c_pointers) * n_local]."""
+    (rows, k), (nb, kb) = a.shape, b_local.shape
+    if kb != k or rows != m or nb != n_local:
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b_local.shape)}, block {m} x {n_local}")
+    ranks = len(c_pointers)
+    array = (ctypes.c_void_p * ranks)(*c_pointers)
+    status = native.library().krn_b200_gemm_tn_gather(
+        _type_of(a), c_type, _pointer(a), _pointer(b_local), array, ranks, rank, m, n_local, k, _pitch(a), _pitch(b_local),
+        ldc, _stream(stream))
+    native.check(status, "column-sharded tile matrix product")
+
+
 def gemm_fp8_blockscaled_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: Any = None) -> None:
     """c = sum_kb sa[:, kb] * sb[n // 128, kb] * (a8[:, kb] @ b8[:, kb]^T); a, b e4m3 codes, scales f32."""
     (m, k), (n, kb) = a.shape, b.shape

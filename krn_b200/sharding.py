@@ -54,3 +54,36 @@ def gather_columns(c_local: Any, slabs: Any, c_full: Any, world: int, group: Any
     else:
         m, width = c_local.shape
         c_full.view(m, world, width).copy_(slabs.permute(1, 0, 2))
+
+
+class GatheredProduct:
+    """C = A @ B^T sharded by output columns with the all-gather fused into the product kernel.
+
+    Every rank allocates its full C in symmetric memory (torch's `_symmetric_memory`: CUDA virtual-memory allocations
+    mapped into every peer over NVLink) and calls `run(a, b_local)`: the kernel stores this rank's column block into
+    all ranks' C from its epilogue, tile by tile, and a device-side barrier across the ranks follows on the same
+    stream. After `run` returns (stream-ordered) `self.c` holds the whole product on every rank."""
+
+    def __init__(self, m: int, n: int, dtype: Any, group: Any = None) -> None:
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.m, self.n = m, n
+        begin, end = column_block(n, self.rank, self.world, 64)
+        self.n_local = end - begin
+        self.c = symm.empty((m, n), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.c, self.group)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+        from krn_b200.runtime import native
+
+        self.c_type = {torch.bfloat16: native.BF16, torch.float16: native.F16, torch.float32: native.F32}[dtype]
+
+    def run(self, a: Any, b_local: Any, stream: Any = None) -> Any:
+        from krn_b200.runtime import calls
+
+        calls.gemm_tn_gather(a, b_local, self.pointers, self.rank, self.m, self.n_local, self.n, self.c_type, stream)
+        self.handle.barrier()
+        return self.c

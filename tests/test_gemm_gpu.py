@@ -164,3 +164,29 @@ def test_config_two_statistics_at_full_size(cuda) -> None:
     calls.gemm_tn(a, b, c32)
     torch.cuda.synchronize()
     assert float((c32.double() @ ones - rhs).norm() / rhs.norm()) < 1e-5
+
+
+def test_column_sharded_product_stores_into_every_destination(cuda) -> None:
+    """The sharded entry point on one GPU: two "ranks" are two launches on the same device, each storing its column
+    block into both destination buffers (which stand in for the ranks' copies of C). Both copies must equal the
+    unsharded product bit for bit, and nothing outside a block's columns may be touched by the other launch."""
+    torch = cuda
+    m, n, k, ranks = 300, 512, 328, 2
+    rng = np.random.default_rng(17)
+    aw = o.bf16_words(rng.integers(-4, 5, (m, k)).astype(np.float32))
+    bw = o.bf16_words(rng.integers(-4, 5, (n, k)).astype(np.float32))
+    a, b = to_device(torch, aw, "bf16"), to_device(torch, bw, "bf16")
+    copies = [torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(ranks)]
+    pointers = [int(c.data_ptr()) for c in copies]
+    width = n // ranks
+    for rank in range(ranks):
+        calls.gemm_tn_gather(a, b[rank * width:(rank + 1) * width], pointers, rank, m, width, n, native.BF16)
+        torch.cuda.synchronize()
+        other = slice((1 - rank) * width, (2 - rank) * width)
+        if rank == 0:
+            assert all(bool(torch.isnan(c[:, other].float()).all()) for c in copies)  # the other block is untouched
+    want = o.gemm(aw, bw, ab_type=o.BF16, c_type=o.BF16, threads=8)
+    for c in copies:
+        np.testing.assert_array_equal(to_words(torch, c, "bf16"), want)
+    with pytest.raises(Exception, match="whole number of 128-byte store"):
+        calls.gemm_tn_gather(a, b[:200], pointers, 0, m, 200, n, native.BF16)
