@@ -68,6 +68,14 @@ int krn_b200_device_status(int* code, int* site, unsigned int* block);
 int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
                      int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
+/* C[M,N] = A[M,K] * B[K,N]: the same product with b stored row-major as (K, N), the form the reference's tile example
+ * writes (`acc += a[rows, ks] @ b[ks, cols]`, examples/04_libraries/01_gemm_tiles.py:35-40). The b tile reaches the
+ * tensor cores as an MN-major operand (64-column x 64-row swizzled boxes), so no transposed copy of b is made.
+ * ldb is the pitch of a K row of b (>= N). Everything else as krn_b200_gemm_tn, including the unaligned path and
+ * K == 0. */
+int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                     int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
 /* The same product sharded by output columns over the GPUs of one node, with the all-gather of the output
  * columns done by the kernel itself: rank `rank` of `ranks` multiplies A[M,K] by ITS rows of B (b: [n_local, K])
  * and its epilogue stores the column block [rank * n_local, (rank + 1) * n_local) into EVERY rank's C —

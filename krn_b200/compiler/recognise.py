@@ -4,8 +4,9 @@ The reference renders every IR statement as CUDA text (src/krn/compiler/emit.py)
 generator, so a kernel either IS one of the contractions the library implements or it is refused before anything is
 launched ("never ignore it silently", the reference's refusal policy, AGENTS.md:17). Two patterns:
 
-* tile matrix product — `acc = zeros(f32, bm, bn)`, one K loop of `acc += a[rows, ks] @ b[cols, ks].transpose()`,
-  `c[rows, cols] = acc.to(T)` (examples/04_libraries/01_gemm_tiles.py:35-40 with the transposed operand);
+* tile matrix product — `acc = zeros(f32, bm, bn)`, one K loop of `acc += a[rows, ks] @ b[ks, cols]`
+  (examples/04_libraries/01_gemm_tiles.py:35-40) or of `acc += a[rows, ks] @ b[cols, ks].transpose()`, then
+  `c[rows, cols] = acc.to(T)`;
 * flash attention — the statement sequence of examples/04_libraries/08_flash_attention.py:44-59, optionally with a
   leading batch axis and grouped kv heads (`k[head // g, ...]`)."""
 
@@ -22,7 +23,7 @@ TARGET = "sm_100a"
 
 @dataclass(frozen=True)
 class GemmPlan:
-    """`c = a @ b^T`: a (M, K), b (N, K), c (M, N)."""
+    """`c = a @ b^T` with a (M, K), b (N, K), or — `transposed_b` False — `c = a @ b` with b (K, N); c (M, N)."""
 
     a: str
     b: str
@@ -30,6 +31,7 @@ class GemmPlan:
     operand: Dtype
     output: Dtype
     tile: tuple[int, int, int]
+    transposed_b: bool = True
 
 
 @dataclass(frozen=True)
@@ -89,15 +91,15 @@ def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
         return None
     rhs = step.rhs
     if isinstance(rhs, ir.TileLoad):
-        if len(rhs.index) == 2 and _loop_slice(rhs.index[0], loop) and _block_tile(rhs.index[1], "x") == bn:
-            raise refuse(kernel, "a row-major (K, N) right operand needs an MN-major tensor-core operand this library "
-                                 "does not build yet", "store b as (N, K) and write `a[rows, ks] @ b[cols, ks].transpose()`",
-                         span=step.span)
-        return None
-    if not (isinstance(rhs, ir.Transpose) and isinstance(rhs.operand, ir.TileLoad)):
-        return None
-    b = rhs.operand
-    if len(b.index) != 2 or _block_tile(b.index[0], "x") != bn or not _loop_slice(b.index[1], loop):
+        # `a[rows, ks] @ b[ks, cols]`: b is (K, N) and reaches the tensor cores as an MN-major operand
+        b, transposed_b = rhs, False
+        if len(b.index) != 2 or not _loop_slice(b.index[0], loop) or _block_tile(b.index[1], "x") != bn:
+            return None
+    elif isinstance(rhs, ir.Transpose) and isinstance(rhs.operand, ir.TileLoad):
+        b, transposed_b = rhs.operand, True
+        if len(b.index) != 2 or _block_tile(b.index[0], "x") != bn or not _loop_slice(b.index[1], loop):
+            return None
+    else:
         return None
     value = store.value
     if isinstance(value, ir.Cast):
@@ -115,7 +117,7 @@ def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
     output = kernel.tensor(store.tensor).dtype
     if output.name not in ("bf16", "f16", "f32"):
         raise refuse(kernel, f"{output} outputs are not supported", "store bf16, f16 or f32", span=store.span)
-    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step))
+    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step), transposed_b)
 
 
 def _head_index(e: ir.Expr) -> int | None:

@@ -8,6 +8,7 @@ namespace krnb {
 struct Problem {
   int m, n, k;
   int tiles_m, tiles_n;
+  int b_kn;  // 0: b is (N, K), the operand of `b.transpose()`; 1: b is (K, N), the operand of a plain `a @ b`
 };
 
 // Tile order: bands of 8 tile rows walked column by column, so that the tiles in flight at any time

@@ -413,6 +413,7 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
   p.k = int(k);
   p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
+  p.b_kn = 0;
   Scales scales;
   scales.sa = sa;
   scales.sb = sb;

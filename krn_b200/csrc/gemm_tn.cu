@@ -141,13 +141,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (CTA_GROUP == 1) {
             mbar_arrive_expect_tx(full_bar + 8 * stage, L::kStageBytes);
             tma_load_2d(a_dst, &map_a, kb * kBK, row_a, full_bar + 8 * stage);
-            tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
+            if (!p.b_kn) {
+              tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
+            } else {
+              // b is (K, N): 64-column x 64-row boxes, N contiguous; one box per 64 output columns
+              for (int blk = 0; blk < L::kBRows / 64; ++blk)
+                tma_load_2d(b_dst + blk * 8192, &map_b, row_b + blk * 64, kb * kBK, full_bar + 8 * stage);
+            }
           } else {
             // Both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both.
             if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * L::kStageBytes);
             const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
             tma_load_2d_pair(a_dst, &map_a, kb * kBK, row_a, leader_full);
-            tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
+            if (!p.b_kn) {
+              tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
+            } else {
+              for (int blk = 0; blk < L::kBRows / 64; ++blk)
+                tma_load_2d_pair(b_dst + blk * 8192, &map_b, row_b + blk * 64, kb * kBK, leader_full);
+            }
           }
           if (++stage == L::kStages) {
             stage = 0;
@@ -159,7 +170,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc(ab_format, ab_format, kBM * CTA_GROUP, kBN);
+      const uint32_t idesc = umma_idesc(ab_format, ab_format, kBM * CTA_GROUP, kBN, 0, p.b_kn ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
@@ -178,11 +189,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_fence_after();
           const uint32_t a_addr = stages_addr + stage * L::kStageBytes;
           const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
-          const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::kABytes);
+          // b as (N, K): K-major like a, 32 bytes of K per instruction inside the swizzle span. b as (K, N): an
+          // MN-major operand, 64-column blocks 8192 bytes apart, 8-row K groups 1024 bytes apart, 16 K rows per
+          // instruction = 2048 bytes.
+          const uint64_t b_desc = p.b_kn ? umma_desc_mnmajor_sw128(a_addr + L::kABytes, 8192, 1024)
+                                         : umma_desc_kmajor_sw128(a_addr + L::kABytes);
+          const uint64_t b_step = p.b_kn ? uint64_t(2048 >> 4) : 2;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            // 32 bytes of K per instruction: step the 16-byte-unit start address inside the swizzle span
-            umma_ss<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
+            umma_ss<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_desc + 2 * ks, b_desc + b_step * ks, idesc,
                                                 (kb > 0 || ks > 0) ? 1u : 0u);
           }
           if constexpr (CTA_GROUP == 1) {
@@ -340,7 +355,7 @@ __device__ __forceinline__ float load_16bit(const uint16_t* p, bool bf16) {
 
 __global__ void __launch_bounds__(256)
 gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, void* __restrict__ c, int m,
-                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type) {
+                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type, bool b_kn) {
   __shared__ float as[16][65], bs[16][65];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
@@ -349,7 +364,8 @@ gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restr
     for (int i = threadIdx.x; i < 64 * 16; i += 256) {
       const int r = i >> 4, kk = i & 15;
       as[kk][r] = (row0 + r < m && k0 + kk < k) ? load_16bit(a + (long long)(row0 + r) * lda + k0 + kk, in_bf16) : 0.f;
-      bs[kk][r] = (col0 + r < n && k0 + kk < k) ? load_16bit(b + (long long)(col0 + r) * ldb + k0 + kk, in_bf16) : 0.f;
+      const long long b_at = b_kn ? (long long)(k0 + kk) * ldb + col0 + r : (long long)(col0 + r) * ldb + k0 + kk;
+      bs[kk][r] = (col0 + r < n && k0 + kk < k) ? load_16bit(b + b_at, in_bf16) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -404,10 +420,12 @@ int gemm_pair_mode(int64_t m) {
 // destination d (each a row-major matrix of n_total columns with pitch ldc).
 static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type, const void* a, const void* b,
                          void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m,
-                         int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream) {
+                         int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream,
+                         bool b_kn = false) {
   using namespace krnb;
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
   Problem p;
+  p.b_kn = b_kn ? 1 : 0;
   p.m = int(m);
   p.n = int(n);
   p.k = int(k);
@@ -423,10 +441,15 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
     uint32_t box[2] = {64, uint32_t(kBM)};
     if (int rc = encode_tensor_map(&map_a, ab_dt, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  {
+  if (!b_kn) {
     uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
     uint64_t strides[1] = {uint64_t(ldb) * 2};
     uint32_t box[2] = {64, uint32_t(kBN / group)};
+    if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  } else {
+    uint64_t dims[2] = {uint64_t(n), uint64_t(k)};
+    uint64_t strides[1] = {uint64_t(ldb) * 2};
+    uint32_t box[2] = {64, 64};
     if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
   }
   Destinations dst;
@@ -454,8 +477,9 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
   return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, fmt, stream);
 }
 
-extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
-                                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
+// Argument checks, the K == 0 and unaligned cases and the launch, shared by the two layouts of b.
+static int product(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                   int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle, bool b_kn) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
@@ -476,7 +500,7 @@ extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const vo
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
-  if (ldc < n || (k > 0 && (lda < k || ldb < k))) {
+  if (ldc < n || (k > 0 && (lda < k || ldb < (b_kn ? n : k)))) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row (lda %lld, ldb %lld, ldc %lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
   }
@@ -500,14 +524,24 @@ extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const vo
     const dim3 grid(unsigned((n + 63) / 64), unsigned((m + 63) / 64), 1);
     gemm_tn_unaligned_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b),
                                                        c, int(m), int(n), int(k), lda, ldb, ldc,
-                                                       ab_type == KRN_B200_BF16, c_type);
+                                                       ab_type == KRN_B200_BF16, c_type, b_kn);
     KRNB_CUDA(cudaGetLastError());
     return KRN_B200_OK;
   }
 
   const int group = gemm_pair_mode(m);
   void* destinations[1] = {c};
-  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream);
+  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream, b_kn);
+}
+
+extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
+                                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
+  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, false);
+}
+
+extern "C" int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
+                                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
+  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, true);
 }
 
 extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank,

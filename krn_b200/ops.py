@@ -22,6 +22,13 @@ def matmul_nt(a: Any, b: Any, out: Any, stream: Any = None) -> Any:
     return out
 
 
+def matmul(a: Any, b: Any, out: Any, stream: Any = None) -> Any:
+    """out[M, N] = a[M, K] @ b[K, N], b row-major — the operand order of the reference's `lib.matmul`
+    (src/krn/lib/lib.py:580-615)."""
+    calls.gemm_nn(_raw(a), _raw(b), _raw(out), _stream(stream))
+    return out
+
+
 @dataclass(frozen=True)
 class QMatrix:
     """A block-scaled FP8 matrix on the device: e4m3fn `codes` (rows, K) and fp32 `scales` with one scale per

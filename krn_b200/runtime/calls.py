@@ -57,6 +57,19 @@ def gemm_tn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
     native.check(status, "tile matrix product")
 
 
+def gemm_nn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
+    """c[M, N] = a[M, K] @ b[K, N] with f32 accumulation (b row-major, not transposed); types as `gemm_tn`."""
+    (m, k), (kb, n) = a.shape, b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    if _type_of(a) != _type_of(b):
+        raise TypeError("both operands must have the same element type")
+    status = native.library().krn_b200_gemm_nn(
+        _type_of(a), _type_of(c), _pointer(a), _pointer(b), _pointer(c), m, n, k, _pitch(a), _pitch(b), _pitch(c),
+        _stream(stream))
+    native.check(status, "tile matrix product")
+
+
 def gemm_tn_gather(a: Any, b_local: Any, c_pointers: list[int], rank: int, m: int, n_local: int, ldc: int, c_type: int,
                    stream: Any = None) -> None:
     """This rank's column block of c = a @ b^T, stored by the kernel's epilogue into every rank's full C.

@@ -221,14 +221,17 @@ class B200Launcher(api.Launcher):
         a, b, c = (_raw(named[n]) for n in (plan.a, plan.b, plan.c))
         needed = infer_geometry(captured, shapes)
         self._check_cover(captured, launch, needed)
-        if a.shape[1] != b.shape[1] or tuple(c.shape) != (a.shape[0], b.shape[0]):
+        b_k, b_n = (b.shape[1], b.shape[0]) if plan.transposed_b else (b.shape[0], b.shape[1])
+        if a.shape[1] != b_k or tuple(c.shape) != (a.shape[0], b_n):
             raise ValueError(f"{captured.name}: shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, "
                              f"c {tuple(c.shape)}")
         explanation = api.Explanation(
-            captured.name, f"tile matrix product c = a @ b^T, {plan.operand} operands, {plan.output} output, "
-            f"declared tile {plan.tile}", launch or needed, "krn_b200_gemm_tn (tcgen05, 256x256 CTA-pair tiles)",
+            captured.name, f"tile matrix product c = a @ b{'^T' if plan.transposed_b else ''}, {plan.operand} operands, "
+            f"{plan.output} output, declared tile {plan.tile}", launch or needed,
+            f"krn_b200_gemm_{'tn' if plan.transposed_b else 'nn'} (tcgen05, 256x256 CTA-pair tiles)",
             ("the library chooses its own CTA tiling; the declared tile only shapes the inferred geometry",))
-        return Call(lambda stream: calls.gemm_tn(a, b, c, stream.raw), explanation)
+        product = calls.gemm_tn if plan.transposed_b else calls.gemm_nn
+        return Call(lambda stream: product(a, b, c, stream.raw), explanation)
 
     def _attention(self, captured, plan: AttentionPlan, named, shapes, launch) -> Call:
         q, k, v, o = (_raw(named[n]) for n in (plan.q, plan.k, plan.v, plan.o))

@@ -38,6 +38,16 @@ def matmul_nn(t: Tiling, a: Matrix[f16], b: Matrix[f16], c: Matrix[f16]) -> None
     c[rows, cols] = acc.to(f16)
 
 
+@kernel
+def matmul_mixed(t: Tiling, a: Matrix[bf16], b: Matrix[f16], c: Matrix[f32]) -> None:
+    """Mixed 16-bit operand types: no tensor-core kind multiplies them."""
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk):
+        acc += a[rows, ks] @ b[cols, ks].transpose()
+    c[rows, cols] = acc.to(f32)
+
+
 @struct
 class Heads:
     bq: Const[int] = 16

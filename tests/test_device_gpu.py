@@ -45,6 +45,25 @@ def test_configured_gemm_call_forms_and_ragged_shapes(device) -> None:
         np.testing.assert_array_equal(got, outputs[0].to_host().view(np.uint16))
 
 
+def test_reference_example_form_with_row_major_b(device) -> None:
+    """`acc += a[rows, ks] @ b[ks, cols]` on the reference example's 50 x 38 x 70 f16 shapes
+    (examples/04_libraries/01_gemm_tiles.py:35-52) and on an aligned shape that takes the tensor-core kernel."""
+    rng = np.random.default_rng(3)
+    for m, n, k in ((50, 38, 70), (260, 136, 72)):
+        a16 = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+        b16 = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+        a, b, c = device.to_device(a16), device.to_device(b16), device.empty(krn.f16, m, n)
+        t = K.Tiling(bm=16, bn=16, bk=8)
+        assert "krn_b200_gemm_nn" in str(K.matmul_nn.explain(t, a, b, c))
+        K.matmul_nn(t, a, b, c)
+        ops.matmul(a, b, c2 := device.empty(krn.f16, m, n))
+        device.default_stream.record().wait(TIMEOUT)
+        want = o.gemm(a16.view(np.uint16), np.ascontiguousarray(b16.T).view(np.uint16), ab_type=o.F16, c_type=o.F16)
+        got = c.to_host().view(np.uint16)
+        assert o.rel_frobenius(got.view(np.float16).astype(np.float32), want.view(np.float16).astype(np.float32)) < 1e-2
+        np.testing.assert_array_equal(got, c2.to_host().view(np.uint16))
+
+
 def test_range_loop_f16_f32_and_explain(device) -> None:
     rng = np.random.default_rng(2)
     a16, b16 = rng.uniform(-1, 1, (130, 104)).astype(np.float16), rng.uniform(-1, 1, (72, 104)).astype(np.float16)

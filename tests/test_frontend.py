@@ -56,10 +56,13 @@ def test_recognise_gemm_forms() -> None:
     assert plan == GemmPlan("a", "b", "c", krn.bf16, krn.bf16, (128, 128, 32))
     plan = recognise(capture(K.matmul_nt_f16_f32.fn))
     assert plan == GemmPlan("a", "b", "c", krn.f16, krn.f32, (32, 64, 16))
+    # the reference example's own form, b stored (K, N)
+    plan = recognise(capture(K.matmul_nn.fn, K.Tiling()))
+    assert plan == GemmPlan("a", "b", "c", krn.f16, krn.f16, (128, 128, 32), transposed_b=False)
     with pytest.raises(TargetError) as error:
-        recognise(capture(K.matmul_nn.fn, K.Tiling()))
+        recognise(capture(K.matmul_mixed.fn, K.Tiling()))
     text = str(error.value)
-    assert "is not available on sm_100a" in text and "Instead:" in text and "transpose()" in text
+    assert "is not available on sm_100a" in text and "Instead:" in text and "convert one operand" in text
     assert "tile_kernels.py" in text and "^" in text  # compiler-style location with a caret
 
 

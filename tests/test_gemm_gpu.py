@@ -126,6 +126,55 @@ def test_shapes_tma_cannot_describe_match_the_oracle_bit_for_bit(cuda, m, n, k, 
     np.testing.assert_array_equal(got, want)
 
 
+def run_nn(torch, aw, bw_kn, dtype, output):
+    """`a @ b` with b stored (K, N)."""
+    m, n = aw.shape[0], bw_kn.shape[1]
+    a, b = to_device(torch, aw, dtype), to_device(torch, np.ascontiguousarray(bw_kn), dtype)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=getattr(torch, TORCH_OF[output]))
+    calls.gemm_nn(a, b, c)
+    torch.cuda.synchronize()
+    return to_words(torch, c, output)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (384, 512, 1024), (1024, 1024, 1024), (50, 40, 72), (130, 72, 104),
+                                   (257, 136, 40), (130, 264, 40), (1, 8, 8), (129, 8, 4096), (300, 520, 328)])
+@pytest.mark.parametrize("dtype,output", [("bf16", "bf16"), ("f16", "f32")])
+def test_row_major_right_operand_against_oracle(cuda, m, n, k, dtype, output) -> None:
+    """`a[rows, ks] @ b[ks, cols]`, the form of examples/04_libraries/01_gemm_tiles.py:35-40: the same numbers as
+    the transposed form on the transposed matrix."""
+    aw, bw = operands(m, n, k, dtype, seed=1)
+    got = run_nn(cuda, aw, bw.T, dtype, output)
+    check(got, aw, bw, dtype, output, k)
+    # both layouts drive the tensor cores with the same operand values in the same order
+    np.testing.assert_array_equal(got, run(cuda, aw, bw, dtype, output))
+
+
+@pytest.mark.parametrize("m,n,k", [(50, 38, 70), (130, 257, 33), (7, 3, 5)])
+def test_row_major_right_operand_unaligned_is_bit_identical_to_the_oracle(cuda, m, n, k) -> None:
+    aw, bw = operands(m, n, k, "bf16", seed=2)
+    got = run_nn(cuda, aw, bw.T, "bf16", "bf16")
+    np.testing.assert_array_equal(got, o.gemm(aw, bw, ab_type=o.BF16, c_type=o.BF16))
+
+
+def test_row_major_right_operand_exact_and_ragged_views(cuda) -> None:
+    torch = cuda
+    rng = np.random.default_rng(11)
+    m, n, k = 300, 520, 328
+    a = rng.integers(-4, 5, (m, k)).astype(np.float32)
+    b = rng.integers(-4, 5, (n, k)).astype(np.float32)
+    aw, bw = o.bf16_words(a), o.bf16_words(b)
+    want = o.gemm(aw, bw, ab_type=o.BF16, c_type=o.F32, threads=8)
+    np.testing.assert_array_equal(run_nn(torch, aw, bw.T, "bf16", "f32"), want)
+    # b as a column window of a wider (K, N') matrix: the pitch is not the row length
+    wide = torch.zeros((k, n + 64), device="cuda", dtype=torch.bfloat16)
+    wide[:, 8:8 + n] = to_device(torch, np.ascontiguousarray(bw.T), "bf16")
+    big = torch.full((m + 8, n + 8), 3.0, device="cuda", dtype=torch.float32)
+    calls.gemm_nn(to_device(torch, aw, "bf16"), wide[:, 8:8 + n], big[:m, :n])
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(big[:m, :n].cpu().numpy(), want)
+    assert bool((big[m:] == 3).all()) and bool((big[:, n:] == 3).all())
+
+
 def test_refusals_are_raised_before_launch(cuda) -> None:
     torch = cuda
     b = torch.zeros((8, 12), device="cuda", dtype=torch.bfloat16)
