@@ -49,6 +49,9 @@ NCU_TRAFFIC_BYTES = {"gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(
                      "attn_fwd": int(137.6e6 * 671.1 / 167.8), "attn_decode": int(690.2e6)}
 
 
+L2_BYTES = 126 * 10**6
+
+
 def measured_peaks() -> tuple[dict, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -111,6 +114,19 @@ class Workload:
     def scale(self, work: float, ms: float) -> float:
         return work / (ms * 1e-3) / 1e12  # flop -> TFLOP/s (bytes -> GB/s overridden below)
 
+    @staticmethod
+    def rotation(set_bytes: int) -> int:
+        """How many copies of a step's tensors to rotate through so that consecutive steps never find their inputs in
+        the 126 MB L2: one when a single set is already twice the L2, else enough for 384 MB in total."""
+        return 1 if set_bytes >= 2 * L2_BYTES else -(-3 * L2_BYTES // max(1, set_bytes))
+
+    @staticmethod
+    def l2_note(what: str, set_bytes: int, copies: int) -> str:
+        size = f"{what} ({set_bytes / 2**20:.0f} MiB per rank)"
+        if copies == 1:
+            return f"{size} exceed the 126 MB L2; no flush between steps"
+        return f"{size} would fit the 126 MB L2: steps rotate through {copies} copies ({copies * set_bytes / 2**20:.0f} MiB)"
+
     def peak(self, peaks: dict) -> tuple[float, str]:
         return peaks["bf16_tflops"], "burst (cuBLAS bf16 8192^3)"
 
@@ -152,8 +168,9 @@ class GemmBf16(Workload):
         gather = ("all-gather of the output columns fused into the product kernel (TMA stores into every rank's C over "
                   "NVLink) + device barrier" if self.fused else "NCCL all-gather of the output columns + re-layout kernel")
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
-                "sharding": f"N-column blocks x{self.world}, {gather}",
-                "l2": "operands and output (384 MiB) exceed the 126 MB L2; no flush between steps"}
+                "sharding": f"N-column blocks x{self.world}, {gather}" if self.world > 1 else "one GPU, no exchange",
+                "l2": self.l2_note("operands and output", 2 * (self.m * self.k + self.n_local * self.k + self.m * (
+                    self.n if self.world > 1 else self.n_local)), 1)}
 
     def work(self) -> float:
         return 2.0 * self.m * self.n * self.k
@@ -240,8 +257,10 @@ class GemmFp8(Workload):
     @property
     def config(self) -> dict:
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
-                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns",
-                "l2": "operands and output (736 MiB) exceed the 126 MB L2; no flush between steps"}
+                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns" if self.world > 1
+                else "one GPU, no exchange",
+                "l2": self.l2_note("operands and output", self.m * self.k + self.n_local * self.k + 2 * self.m * (
+                    self.n if self.world > 1 else self.n_local), 1)}
 
     def work(self) -> float:
         return 2.0 * self.m * self.n * self.k
@@ -310,11 +329,16 @@ class AttnFwd(Workload):
         del q, k, v
         self.o = torch.empty_like(self.q)
         self.scale_log2 = math.log2(math.e) / math.sqrt(self.d)
+        self.set_bytes = sum(t.numel() * 2 for t in (self.q, self.k, self.v, self.o))
+        self.sets = [(self.q, self.k, self.v, self.o)]
+        for _ in range(self.rotation(self.set_bytes) - 1 if self.batch_local else 0):
+            self.sets.append(tuple(t.clone() for t in self.sets[0]))
+        self.turn = 0
 
     @property
     def config(self) -> dict:
         return {"workload": self.description, "sharding": f"(batch, kv head) units x{self.world}, no collective",
-                "l2": "Q, K, V, O (640 MiB) exceed the 126 MB L2; no flush between steps"}
+                "l2": self.l2_note("Q, K, V, O", self.set_bytes, len(self.sets))}
 
     def work(self) -> float:
         return 4.0 * self.batch * self.hq * self.d * self.seq * (self.seq + 1) / 2
@@ -322,9 +346,14 @@ class AttnFwd(Workload):
     def kernel_work(self) -> float:
         return self.work() * self.batch_local / self.batch
 
-    def step(self, calls) -> None:
+    def run(self, calls, tensors) -> None:
         if self.batch_local:
-            calls.attention_forward(self.q, self.k, self.v, self.o, self.scale_log2, True, self.torch.cuda.current_stream())
+            q, k, v, o = tensors
+            calls.attention_forward(q, k, v, o, self.scale_log2, True, self.torch.cuda.current_stream())
+
+    def step(self, calls) -> None:
+        self.run(calls, self.sets[self.turn % len(self.sets)])
+        self.turn += 1
 
     kernel_only = step
 
@@ -336,7 +365,7 @@ class AttnFwd(Workload):
     def e2e_step(self, calls) -> None:
         for dst, src in zip((self.q, self.k, self.v), self.host_in):
             dst.copy_(src, non_blocking=True)
-        self.step(calls)
+        self.run(calls, self.sets[0])
         self.host_out.copy_(self.o, non_blocking=True)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
@@ -395,11 +424,16 @@ class AttnDecode(Workload):
         self.scale_log2 = math.log2(math.e) / math.sqrt(self.d)
         self.workspace = torch.empty(calls.decode_workspace_bytes(self.local, self.hq, self.d, 8192), device="cuda",
                                      dtype=torch.uint8)
+        self.set_bytes = int(self.kernel_work())
+        self.pools = [(self.k_pages, self.v_pages)]
+        for _ in range(self.rotation(self.set_bytes) - 1):
+            self.pools.append((self.k_pages.clone(), self.v_pages.clone()))
+        self.turn = 0
 
     @property
     def config(self) -> dict:
         return {"workload": self.description, "sharding": f"sequences balanced by length x{self.world}, no collective",
-                "l2": "the cache pages read per step (~0.6 GB) exceed the 126 MB L2; no flush between steps"}
+                "l2": self.l2_note("the cache pages read per step", self.set_bytes, len(self.pools))}
 
     def _bytes(self, tokens: int, sequences: int) -> float:
         return tokens * 2.0 * self.hkv * self.d + 2.0 * sequences * self.hq * self.d * 2 + 4.0 * tokens / self.page
@@ -417,7 +451,9 @@ class AttnDecode(Workload):
         return peaks["hbm_gbs"], "STREAM-style copy bandwidth"
 
     def step(self, calls) -> None:
-        calls.attention_decode_fp8_paged(self.q, self.k_pages, self.v_pages, self.table, self.lens, self.k_scale,
+        k_pages, v_pages = self.pools[self.turn % len(self.pools)]
+        self.turn += 1
+        calls.attention_decode_fp8_paged(self.q, k_pages, v_pages, self.table, self.lens, self.k_scale,
                                          self.v_scale, self.o, self.scale_log2, 8192, self.workspace,
                                          self.torch.cuda.current_stream())
 
@@ -551,7 +587,7 @@ def main() -> int:
     achieved = workload.scale(workload.kernel_work(), kernel_ms)
     peak, peak_note = workload.peak(peaks)
     roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit, "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES[workload.name], "peak_kind": f"{peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
+                "traffic": None if args.size or world > 1 else NCU_TRAFFIC_BYTES[workload.name], "peak_kind": f"{peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
     if workload.bound == "tensor":
         nominal = 4500.0 if workload.dtype.startswith("fp8") else 2250.0
         roofline["frac_of_nominal_dense_peak"] = achieved / nominal
