@@ -12,16 +12,29 @@
 // (src/krn/facts/targets.py:127-138) — and no dequantised copy of an operand ever exists. The reference has
 // no implementation of this product (QMatrix / QTile are signatures only, src/krn/frontend/memory.py:173-193).
 //
-// Roles per CTA (384 threads = 3 warpgroups): warp 0 TMA producer, warp 1 MMA issuer (warps 2, 3 idle; the
-// group gives its registers away with setmaxnreg), warps 4..11 promotion + store with 232 registers each. A
-// promotion warp owns 32 rows (its tensor-memory lane quarter) x 128 columns (one scale block of B), i.e.
-// 128 accumulators per thread.
+// Roles per CTA (384 threads = 3 warpgroups): warp 0 TMA producer, warp 1 MMA issuer, warps 2-3 scale
+// loaders (the group gives registers away with setmaxnreg), warps 4..11 promotion + store with 232 registers
+// each. A promotion warp owns 32 rows (its tensor-memory lane quarter) x 128 columns (one scale block of B),
+// i.e. 128 accumulators per thread.
 //
-// The hand-off between the MMA warp and the promotion warps happens every K block, so its latency decides the
-// throughput. Measured on B200 at M=8192, N=28672, K=8192: one CTA per tile (cta_group::1) 2.35 ms; CTA pairs
-// (cta_group::2, kept below as a template instance) 3.98 ms, because every hand-off then crosses the cluster;
-// splitting a stage into two N=128 halves over four partial buffers 4.26 ms, because A is then read from
-// shared memory twice per stage. The dispatch therefore uses one CTA per tile and two 256-column partials.
+// What the measurements on B200 (M=8192, N=28672, K=8192) say about this kernel:
+//  * Operand feed decides the tile shape. One CTA per 128x256 tile moves 48 KB per K block through L2 and
+//    shared memory and tops out at 1.40 ms even with the promotion removed; a CTA pair on a 256x256 tile
+//    (cta_group::2, each CTA loads 128 rows of A and 128 rows of B) moves 32 KB and reaches 1.27-1.32 ms with
+//    the promotion removed. Pairs are therefore used whenever M > 128.
+//  * The pair hands a partial buffer back across the cluster every K block. With a release-scope remote
+//    arrive each hand-back stalled its warp ~1100 cycles (3.98 ms in total); the relaxed arrive is enough
+//    here (see mbar_arrive_cluster_relaxed) and brought the pair to 2.0 ms.
+//  * Per-row scale loads straight from global memory (32 lanes, 32 cache lines, every K block) cost 0.15-0.4 ms:
+//    two otherwise idle warps now fetch eight K blocks of row scales at a time (one 32-byte sector per row)
+//    into a small shared-memory ring, transposed so that a promotion warp reads its 32 scales without conflicts.
+//  * Two tcgen05.ld are kept in flight per wait, so a 128-column strip costs two round trips instead of four.
+//  * With all of that the kernel runs at 1.92-1.98 ms (1950-2000 TFLOP/s; 2.35 ms before). A cycle trace of one
+//    CTA shows what is left: per K block a promotion warp is busy ~950 cycles (barrier poll, two tensor-memory
+//    round trips, 64 packed fmas, hand-back) against 540 cycles of tensor-core work, and every poll or
+//    shared-memory read on that chain costs 100-250 cycles while the tensor cores and TMA keep shared memory busy.
+//    Tried without gain: polling with test_wait, unrolling the issuing thread over the stage ring, fetching the
+//    next block's scale early (the in-order warp then waits on that load in front of its fmas), scalar fmas.
 #include "gemm_common.cuh"
 
 #include <cstdlib>
@@ -32,9 +45,10 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 128;  // FP8 codes per stage row = one scale block
-constexpr int kThreads = 384;  // three warpgroups: {producer, MMA, 2 idle}, promotion x 2
+constexpr int kThreads = 384;  // three warpgroups: {producer, MMA, 2 scale loaders}, promotion x 2
 constexpr int kPromotionWarps = 8;
 constexpr int kTmemColumns = 512;  // two 256-column partial accumulators
+constexpr int kScaleChunk = 8;     // K blocks of row scales per ring slot (8 floats = one 32-byte sector per row)
 
 template <int CTA_GROUP>
 struct Layout {
@@ -42,11 +56,13 @@ struct Layout {
   static constexpr int kABytes = kBM * 128;
   static constexpr int kBBytes = kBRows * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = CTA_GROUP == 2 ? 5 : 3;
-  static constexpr int kStoreBytes = kPromotionWarps * 8192;  // per warp: 32 rows x 256 bytes
+  static constexpr int kStages = CTA_GROUP == 2 ? 6 : 4;
+  static constexpr int kStoreBytes = kPromotionWarps * 2048;  // per warp: one 16-row x 128-byte store box
+  static constexpr int kScaleBytes = 2 * kScaleChunk * kBM * 4;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kScaleBytes + kBarrierBytes + 1024;
 };
+static_assert(Layout<2>::kSmemBytes <= 232448 && Layout<1>::kSmemBytes <= 232448, "shared memory budget");
 
 struct Scales {
   const float* sa;
@@ -55,7 +71,13 @@ struct Scales {
   int blocks_n;  // ceil(N / 128)
 };
 
-enum Site { kSiteProducerEmpty = 11, kSiteMmaFull = 12, kSiteMmaPartialEmpty = 13, kSitePromotionFull = 14 };
+enum Site {
+  kSiteProducerEmpty = 11,
+  kSiteMmaFull = 12,
+  kSitePromotionFull = 14,
+  kSiteScaleEmpty = 15,
+  kSitePromotionScale = 16,
+};
 
 __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], int chunk, const uint32_t (&p)[32], float scale) {
   const float2 s2 = make_float2(scale, scale);
@@ -80,12 +102,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const uint32_t stages_addr = base;
   const uint32_t store_addr = base + L::kStages * L::kStageBytes;
-  uint8_t* tail = smem + L::kStages * L::kStageBytes + L::kStoreBytes;
+  float* scale_ring = reinterpret_cast<float*>(smem + L::kStages * L::kStageBytes + L::kStoreBytes);
+  uint8_t* tail = smem + L::kStages * L::kStageBytes + L::kStoreBytes + L::kScaleBytes;
   const uint32_t full_bar = smem_u32(tail);
   const uint32_t empty_bar = full_bar + 8 * L::kStages;
   const uint32_t part_full_bar = empty_bar + 8 * L::kStages;
-  const uint32_t part_empty_bar = part_full_bar + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * L::kStages + 4));
+  const uint32_t scale_full_bar = part_full_bar + 16;
+  const uint32_t scale_empty_bar = scale_full_bar + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * L::kStages + 6));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -98,12 +122,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) {
-      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, 1 + kPromotionWarps * CTA_GROUP);  // producer + hand-back of the partial buffer
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(part_full_bar + 8 * i, 1);
-      mbar_init(part_empty_bar + 8 * i, kPromotionWarps * CTA_GROUP);
+      mbar_init(scale_full_bar + 8 * i, 2);                  // the two loader warps
+      mbar_init(scale_empty_bar + 8 * i, kPromotionWarps);   // this CTA's promotion warps
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -162,28 +187,31 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    // One thread, every instruction waiting for the one before; beside the promotion warps of its scheduler a
+    // barrier poll that succeeds at once still costs it about 250 cycles. So it polls ONE barrier per K block:
+    // `full[stage]` counts the producer's arrive (with the stage's bytes) AND the promotion warps' hand-back of the
+    // partial buffer this K block will overwrite (they arrive on the full barrier of the K block two ahead).
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(kFmtE4M3, kFmtE4M3, kBM * CTA_GROUP, kBN);
+      const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
+      const uint32_t desc_hi = uint32_t(desc0 >> 32);
+      uint32_t a_lo = uint32_t(desc0);
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t it = 0;  // K blocks issued so far, over all tiles: selects the partial buffer
+      uint32_t buf = 0;
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t buf = it & 1u;
-          if (!mbar_wait(part_empty_bar + 8 * buf, ((it >> 1) & 1u) ^ 1u, abort_flag, status, kSiteMmaPartialEmpty) ||
-              !mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * kBN;
-          const uint32_t a_addr = stages_addr + stage * L::kStageBytes;
-          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
-          const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::kABytes);
+          const uint32_t b_lo = a_lo + (L::kABytes >> 4);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            umma_ss<CTA_GROUP, true>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+            umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, idesc, ks > 0 ? 1u : 0u);
           }
           if constexpr (CTA_GROUP == 1) {
             umma_commit(empty_bar + 8 * stage);
@@ -192,44 +220,116 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             umma_commit_pair(empty_bar + 8 * stage, 0x3);
             umma_commit_pair(part_full_bar + 8 * buf, 0x3);
           }
+          buf ^= 1u;
+          a_lo += L::kStageBytes >> 4;
           if (++stage == L::kStages) {
             stage = 0;
             phase ^= 1u;
+            a_lo = uint32_t(desc0);
           }
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    // ---------------------------------------------------------------- row-scale loaders (64 threads)
+    // Ring slot = kScaleChunk K blocks x 128 rows, stored [block][row] so that a promotion warp reads 32
+    // consecutive floats. Each thread fetches the 8 scales of two rows: one 32-byte sector per row.
+    const int tid = int(threadIdx.x) - 64;
+    const bool vector_ok = (reinterpret_cast<uintptr_t>(scales.sa) % 16 == 0) && (scales.ldsa % 4 == 0);
+    uint32_t chunk = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      const int row0 = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
+      for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk) {
+        const uint32_t slot = chunk & 1u;
+        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, ((chunk >> 1) & 1u) ^ 1u, abort_flag, status,
+                                               kSiteScaleEmpty))) {
+          ok = false;
+          break;
+        }
+        float* dst = scale_ring + slot * (kScaleChunk * kBM);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = tid + half * 64;
+          const int row = row0 + r;
+          float v[kScaleChunk];
+#pragma unroll
+          for (int j = 0; j < kScaleChunk; ++j) v[j] = 0.f;
+          if (row < p.m) {
+            const float* src = scales.sa + (long long)row * scales.ldsa + kb0;
+            if (vector_ok && kb0 + kScaleChunk <= num_kb) {
+              const float4 lo = __ldg(reinterpret_cast<const float4*>(src));
+              const float4 hi = __ldg(reinterpret_cast<const float4*>(src) + 1);
+              v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w;
+              v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+            } else {
+#pragma unroll
+              for (int j = 0; j < kScaleChunk; ++j) {
+                if (kb0 + j < num_kb) v[j] = __ldg(src + j);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kScaleChunk; ++j) dst[j * kBM + r] = v[j];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(scale_full_bar + 8 * slot);
+      }
+    }
+  } else {
     // ---------------------------------------------------------------- promotion + store warps
     reg_alloc<232>();
     const int pw = warp - 4;       // 0..7
     const int quarter = warp & 3;  // tensor-memory lane quarter this warp may read
     const int half = pw >> 2;      // which 128-column scale block of the tile
-    const uint32_t my_store = store_addr + pw * 8192;
-    const uint32_t leader_part_empty = CTA_GROUP == 2 ? map_to_cta(part_empty_bar, 0) : part_empty_bar;
+    const uint32_t my_store = store_addr + pw * 2048;
+    const uint32_t leader_full = CTA_GROUP == 2 ? map_to_cta(full_bar, 0) : full_bar;
+    // the first two K blocks overwrite partial buffers nobody has to hand back
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if constexpr (CTA_GROUP == 2) {
+          mbar_arrive_cluster_relaxed(leader_full + 8 * s);
+        } else {
+          mbar_arrive(full_bar + 8 * s);
+        }
+      }
+    }
+    uint32_t handback_stage = 2;  // stage of K block it + 2
+    const float* my_scales = scale_ring + quarter * 32 + lane;
     uint32_t it = 0;
+    uint32_t chunk = 0;
     bool ok = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int tm, tn;
       tile_coords(t, p, tm, tn);
       const int row0 = tm * (kBM * CTA_GROUP) + int(rank) * kBM + quarter * 32;
       const int col0 = tn * kBN + half * 128;
-      const int row = row0 + int(lane);
-      const bool row_ok = row < p.m;
       const int nb = col0 / 128;
       const bool nb_ok = nb < scales.blocks_n;
-      const float* sa_row = scales.sa + (long long)(row_ok ? row : 0) * scales.ldsa;
       const float* sb_row = scales.sb + (long long)(nb_ok ? nb : 0) * scales.ldsb;
 
       float2 acc[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
 
-      float next_scale = (num_kb > 0 && row_ok && nb_ok) ? __ldg(sa_row) * __ldg(sb_row) : 0.f;
+      float next_sb = (num_kb > 0 && nb_ok) ? __ldg(sb_row) : 0.f;  // one address for the whole warp
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const uint32_t buf = it & 1u;
-        const float scale = next_scale;
-        if (kb + 1 < num_kb && row_ok && nb_ok) next_scale = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
+        const uint32_t slot = chunk & 1u;
+        const int in_chunk = kb & (kScaleChunk - 1);
+        if (in_chunk == 0) {
+          if (!__all_sync(0xffffffffu, mbar_wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, abort_flag, status,
+                                                 kSitePromotionScale))) {
+            ok = false;
+            break;
+          }
+        }
+        // rows beyond M hold a zero scale in the ring, so their accumulators stay zero
+        const float scale = my_scales[slot * (kScaleChunk * kBM) + in_chunk * kBM] * next_sb;
+        if (kb + 1 < num_kb && nb_ok) next_sb = __ldg(sb_row + kb + 1);
         if (!__all_sync(0xffffffffu,
                         mbar_wait(part_full_bar + 8 * buf, (it >> 1) & 1u, abort_flag, status, kSitePromotionFull))) {
           ok = false;
@@ -239,72 +339,71 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kBN + half * 128;
         uint32_t p0[32], p1[32];
         tmem_ld_32x32(t_addr, p0);
-        tmem_ld_wait(p0);
         tmem_ld_32x32(t_addr + 32, p1);
+        tmem_ld_wait(p0, p1);
         fma_chunk(acc, 0, p0, scale);
-        tmem_ld_wait(p1);
         tmem_ld_32x32(t_addr + 64, p0);
         fma_chunk(acc, 1, p1, scale);
-        tmem_ld_wait(p0);
         tmem_ld_32x32(t_addr + 96, p1);
-        fma_chunk(acc, 2, p0, scale);
-        tmem_ld_wait(p1);
-        // the partial buffer is fully read: hand it back before the last fmas
+        tmem_ld_wait(p0, p1);
+        // the partial buffer is fully read (its data sits in registers): hand it back before the last fmas
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           if constexpr (CTA_GROUP == 2) {
-            mbar_arrive_cluster(leader_part_empty + 8 * buf);
+            mbar_arrive_cluster_relaxed(leader_full + 8 * handback_stage);
           } else {
-            mbar_arrive(part_empty_bar + 8 * buf);
+            mbar_arrive(full_bar + 8 * handback_stage);
           }
+          if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) mbar_arrive(scale_empty_bar + 8 * slot);
         }
+        if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) ++chunk;
+        if (++handback_stage == L::kStages) handback_stage = 0;
+        fma_chunk(acc, 2, p0, scale);
         fma_chunk(acc, 3, p1, scale);
       }
       if (!ok) break;
 
-      // ---- store this warp's 32 x 128 block: 128-byte rows through swizzled shared memory and TMA
-      constexpr int kStoreChunks = 128 / kChunkCols;        // 2 for 16-bit outputs, 4 for f32
-      constexpr int kChunksPerRound = 2;                     // 8 KB of staging = two 32 x 128-byte boxes
+      // ---- store this warp's 32 x 128 block through 2 KB of swizzled staging: 128-byte strips, 16 rows per TMA box
+      constexpr int kStoreChunks = 128 / kChunkCols;  // 2 for 16-bit outputs, 4 for f32
 #pragma unroll
-      for (int round = 0; round < kStoreChunks / kChunksPerRound; ++round) {
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
+      for (int chunk_index = 0; chunk_index < kStoreChunks; ++chunk_index) {
+        uint32_t packed[32];
+        if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-        for (int c = 0; c < kChunksPerRound; ++c) {
-          const int chunk = round * kChunksPerRound + c;
-          uint32_t packed[32];
-          if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              packed[2 * i] = __float_as_uint(acc[chunk * 16 + i].x);
-              packed[2 * i + 1] = __float_as_uint(acc[chunk * 16 + i].y);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float2 v = acc[chunk * 32 + i];
-              packed[i] = OUT_BF16 ? pack_bf16x2(v.x, v.y) : pack_f16x2(v.x, v.y);
-            }
+          for (int i = 0; i < 16; ++i) {
+            packed[2 * i] = __float_as_uint(acc[chunk_index * 16 + i].x);
+            packed[2 * i + 1] = __float_as_uint(acc[chunk_index * 16 + i].y);
           }
-          const uint32_t row_addr = my_store + c * 4096 + lane * 128;
+        } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
-                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
-                         : "memory");
+          for (int i = 0; i < 32; ++i) {
+            const float2 v = acc[chunk_index * 32 + i];
+            packed[i] = OUT_BF16 ? pack_bf16x2(v.x, v.y) : pack_f16x2(v.x, v.y);
           }
         }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
 #pragma unroll
-          for (int c = 0; c < kChunksPerRound; ++c) {
-            const int col = col0 + (round * kChunksPerRound + c) * kChunkCols;
-            if (row0 < p.m && col < p.n) tma_store_2d(&map_c, col, row0, my_store + c * 4096);
+        for (int rows_half = 0; rows_half < 2; ++rows_half) {
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          if (int(lane >> 4) == rows_half) {
+            const uint32_t row_addr = my_store + (lane & 15u) * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
+                           "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                           : "memory");
+            }
           }
-          tma_store_commit();
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col = col0 + chunk_index * kChunkCols;
+            const int row = row0 + rows_half * 16;
+            if (row < p.m && col < p.n) tma_store_2d(&map_c, col, row, my_store);
+            tma_store_commit();
+          }
         }
       }
     }
@@ -368,6 +467,16 @@ __global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitc
   }
 }
 
+int fp8_pair_mode(int64_t m) {
+  static int env = [] {
+    const char* v = getenv("KRN_B200_FP8_PAIR");
+    return v == nullptr ? -1 : atoi(v);
+  }();
+  if (env == 0) return 1;
+  if (env == 1) return 2;
+  return m > kBM ? 2 : 1;
+}
+
 }  // namespace
 }  // namespace krnb
 
@@ -406,7 +515,9 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
                 "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld bytes, ldc %lld elements)",
                 (long long)lda, (long long)ldb, (long long)ldc);
   }
-  const int group = 1;  // see the measurements at the top of this file
+  // CTA pairs whenever there is more than one 128-row panel (see the measurements at the top of this file);
+  // KRN_B200_FP8_PAIR=0/1 overrides for experiments
+  const int group = fp8_pair_mode(m);
   Problem p;
   p.m = int(m);
   p.n = int(n);
@@ -440,11 +551,13 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
     uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
-    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  if (group == 2) {  // not dispatched today; kept compiling so the measurement above can be repeated
+  if (group == 2) {
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
     if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
   }
   if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
   if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
