@@ -193,16 +193,17 @@ class GemmBf16(Workload):
         calls.gemm_tn(self.a, self.b, self.c_local, self.torch.cuda.current_stream())
 
     def host_buffers(self):
+        """End to end = `krn_b200.streaming.StreamedProduct`: pinned host A, this rank's rows of B and its column block
+        of C, streamed through the device in panels (copies overlap the products of neighbouring panels)."""
+        from krn_b200 import streaming
+
         self.host_in = [t.cpu().pin_memory() for t in (self.a, self.b)]
         self.host_out = self.torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
+        self.streamed = streaming.StreamedProduct(self.m, self.n_local, self.k, self.torch.bfloat16)
         return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
-        self.a.copy_(self.host_in[0], non_blocking=True)
-        self.b.copy_(self.host_in[1], non_blocking=True)
-        self.step(calls)
-        result = self.c_local if self.fused is None else self.fused.c[:, self.columns]
-        self.host_out.copy_(result, non_blocking=True)
+        self.streamed.run(self.host_in[0], self.host_in[1], self.host_out)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         """The faithful block loop (128x128x32 tiles) on the first `cores` block rows of the same problem, one
@@ -283,17 +284,18 @@ class GemmFp8(Workload):
         calls.gemm_fp8_blockscaled_tn(self.a, self.sa, self.b, self.sb, self.c_local, self.torch.cuda.current_stream())
 
     def host_buffers(self):
+        """End to end = `krn_b200.streaming.StreamedFp8Product` over pinned host codes, scales and output."""
+        from krn_b200 import streaming
+
         torch = self.torch
-        self.device_in = [t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in (self.a, self.sa, self.b, self.sb)]
-        self.host_in = [t.cpu().pin_memory() for t in self.device_in]
+        self.host_in = [t.view(torch.uint8).cpu().pin_memory() if t.dtype == torch.float8_e4m3fn else t.cpu().pin_memory()
+                        for t in (self.a, self.sa, self.b, self.sb)]
         self.host_out = torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
+        self.streamed = streaming.StreamedFp8Product(self.m, self.n_local, self.k, self.c_local.dtype)
         return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
-        for dst, src in zip(self.device_in, self.host_in):
-            dst.copy_(src, non_blocking=True)
-        self.step(calls)
-        self.host_out.copy_(self.c_local, non_blocking=True)
+        self.streamed.run(*self.host_in, self.host_out)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         n = columns or 2048
@@ -358,15 +360,19 @@ class AttnFwd(Workload):
     kernel_only = step
 
     def host_buffers(self):
+        """End to end = `krn_b200.streaming.StreamedAttention` over pinned host q, k, v, o, one batch at a time."""
+        from krn_b200 import streaming
+
         self.host_in = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
         self.host_out = self.torch.empty(self.o.shape, dtype=self.o.dtype).pin_memory()
+        if self.batch_local:
+            self.streamed = streaming.StreamedAttention(self.batch_local, self.hq, self.hkv, self.seq, self.d,
+                                                        self.torch.bfloat16, groups=self.batch_local)
         return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
-        for dst, src in zip((self.q, self.k, self.v), self.host_in):
-            dst.copy_(src, non_blocking=True)
-        self.run(calls, self.sets[0])
-        self.host_out.copy_(self.o, non_blocking=True)
+        if self.batch_local:
+            self.streamed.run(*self.host_in, self.host_out, self.scale_log2, True)
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         heads = cores

@@ -161,6 +161,13 @@ int krn_b200_attn_decode_fp8_paged_noalloc(const void* q, const void* k_pages, c
 int krn_b200_scatter_columns(const void* slabs, void* c_full, int64_t m, int64_t n_local, int64_t ranks,
                              int64_t ld_full, int elem_bytes, void* stream);
 
+/* Pitched copy of `rows` rows of `row_bytes` bytes between device memory and page-locked host memory (either
+ * direction, or device to device), enqueued on `stream`: cudaMemcpy2DAsync behind this library's status codes. Used by
+ * the host-operand streaming path to return column slabs of a row-major result into the caller's host matrix. The
+ * reference copies whole tensors only (src/krn/runtime/cuda_backend.py:205-248). */
+int krn_b200_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t row_bytes,
+                     int64_t rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

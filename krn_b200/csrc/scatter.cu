@@ -40,3 +40,21 @@ extern "C" int krn_b200_scatter_columns(const void* slabs, void* c_full, int64_t
   KRNB_CUDA(cudaGetLastError());
   return KRN_B200_OK;
 }
+
+// A pitched copy between any two of {device memory, page-locked host memory}: `rows` rows of `row_bytes` bytes, each
+// side with its own pitch — cudaMemcpy2DAsync behind the library's status convention. The host-operand streaming path
+// uses it to return column slabs of a row-major result straight into the caller's host matrix. Replaces nothing in the
+// reference, whose host copies are whole-tensor (src/krn/runtime/cuda_backend.py:205-248).
+extern "C" int krn_b200_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                                int64_t row_bytes, int64_t rows, void* stream_handle) {
+  using namespace krnb;
+  if (rows <= 0 || row_bytes <= 0) return KRN_B200_OK;
+  if (dst == nullptr || src == nullptr) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null address");
+  if (dst_pitch_bytes < row_bytes || src_pitch_bytes < row_bytes) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "pitch shorter than the row (%lld, %lld < %lld bytes)",
+                (long long)dst_pitch_bytes, (long long)src_pitch_bytes, (long long)row_bytes);
+  }
+  KRNB_CUDA(cudaMemcpy2DAsync(dst, size_t(dst_pitch_bytes), src, size_t(src_pitch_bytes), size_t(row_bytes),
+                              size_t(rows), cudaMemcpyDefault, static_cast<cudaStream_t>(stream_handle)));
+  return KRN_B200_OK;
+}

@@ -155,3 +155,17 @@ def scatter_columns(slabs: Any, c_full: Any, ranks: int, stream: Any = None) -> 
     status = native.library().krn_b200_scatter_columns(_pointer(slabs), _pointer(c_full), m, n_local, ranks,
                                                        _pitch(c_full), element, _stream(stream))
     native.check(status, "column scatter")
+
+
+def copy_matrix(dst: Any, src: Any, stream: Any = None) -> None:
+    """dst[:, :] = src[:, :] for 2-D tensors of one shape and element type whose rows are contiguous but whose row
+    pitches may differ (column slabs of wider matrices); either side may be page-locked host memory."""
+    if tuple(dst.shape) != tuple(src.shape) or dst.element_size() != src.element_size() or len(dst.shape) != 2:
+        raise ValueError(f"copy of {tuple(src.shape)} into {tuple(dst.shape)}")
+    if dst.stride(1) != 1 or src.stride(1) != 1:
+        raise ValueError("rows must be contiguous")
+    rows, columns = dst.shape
+    element = dst.element_size()
+    status = native.library().krn_b200_copy_2d(_pointer(dst), dst.stride(0) * element, _pointer(src),
+                                               src.stride(0) * element, columns * element, rows, _stream(stream))
+    native.check(status, "pitched copy")
