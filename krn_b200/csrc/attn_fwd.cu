@@ -164,27 +164,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_pv = umma_idesc(fmt, fmt, kTileQ, D, 0, 1);
       const int nt[2] = {n0, n1};
 
+      // Descriptors are stepped as 32-bit words: the issuing thread runs one instruction at a time, so every
+      // 64-bit descriptor rebuild it does not do brings the next product forward.
+      const uint64_t kmajor = umma_desc_kmajor_sw128(0);
+      const uint64_t mnmajor = umma_desc_mnmajor_sw128(0, L::kBlockBytes, 1024);
+      const uint32_t kmajor_hi = uint32_t(kmajor >> 32), mnmajor_hi = uint32_t(mnmajor >> 32);
+      const uint32_t q_lo = uint32_t(kmajor) + (q_addr >> 4);
+      const uint32_t k_lo = uint32_t(kmajor) + (k_addr >> 4);
+      const uint32_t v_lo = uint32_t(mnmajor) + (v_addr >> 4);
+
       // S_t = Q_t K^T: D/16 instructions of K = 16; operand rows are 128-byte swizzled, 64 columns per block
       auto issue_s = [&](int t, int stage) {
-        const uint32_t qa = q_addr + t * L::kQBytes;
-        const uint32_t ka = k_addr + stage * L::kKVBytes;
+        const uint32_t qa = q_lo + t * (L::kQBytes >> 4);
+        const uint32_t ka = k_lo + stage * (L::kKVBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * L::kBlockBytes + (ks & 3) * 32;
-          umma_ss<1, false>(tmem_base + t * 128, umma_desc_kmajor_sw128(qa + off), umma_desc_kmajor_sw128(ka + off),
-                            idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * L::kBlockBytes + (ks & 3) * 32) >> 4;
+          umma_ss_halves<1, false>(tmem_base + t * 128, qa + off, ka + off, kmajor_hi, idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * t);
       };
       // O_t += P_t V: 8 instructions of K = 16 keys; A = P_t in tensor memory (8 columns per 16 keys), B = V
       // tile with d contiguous: 64-column blocks kBlockBytes apart (leading), 8-key groups 1024 bytes apart
       auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t va = v_addr + stage * L::kKVBytes;
+        const uint32_t va = v_lo + stage * (L::kKVBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < kTileKV / 16; ++ks) {
-          umma_ts_f16(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
-                      umma_desc_mnmajor_sw128(va + ks * 2048, L::kBlockBytes, 1024), idesc_pv,
-                      (accumulate || ks > 0) ? 1u : 0u);
+          umma_ts_f16_halves(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, va + ks * (2048 >> 4), mnmajor_hi,
+                             idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
         }
       };
 
