@@ -180,7 +180,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * L::kBlockBytes + (ks & 3) * 32) >> 4;
-          umma_ss_halves<1, false>(tmem_base + t * 128, qa + off, ka + off, kmajor_hi, idesc_s, ks > 0 ? 1u : 0u);
+          umma_ss_halves<1, false>(tmem_base + t * 128, qa + off, kmajor_hi, ka + off, kmajor_hi, idesc_s,
+                                   ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * t);
       };

@@ -211,7 +211,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t b_lo = a_lo + (L::kABytes >> 4);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, idesc, ks > 0 ? 1u : 0u);
+            umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, desc_hi, b_lo + 2 * ks, desc_hi, idesc,
+                                            ks > 0 ? 1u : 0u);
           }
           if constexpr (CTA_GROUP == 1) {
             umma_commit(empty_bar + 8 * stage);

@@ -171,6 +171,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(ab_format, ab_format, kBM * CTA_GROUP, kBN, 0, p.b_kn ? 1u : 0u);
+      // Descriptor words: b as (N, K) is K-major like a, 32 bytes of K per instruction inside the swizzle span; b as
+      // (K, N) is an MN-major operand, 64-column blocks 8192 bytes apart, 8-row K groups 1024 bytes apart, 16 K rows
+      // per instruction = 2048 bytes. Only the low word's start-address field moves (32-bit adds: this thread runs one
+      // instruction at a time).
+      const uint64_t a_desc0 = umma_desc_kmajor_sw128(stages_addr);
+      const uint64_t b_desc0 = p.b_kn ? umma_desc_mnmajor_sw128(stages_addr + L::kABytes, 8192, 1024)
+                                      : umma_desc_kmajor_sw128(stages_addr + L::kABytes);
+      const uint32_t a_hi = uint32_t(a_desc0 >> 32), b_hi = uint32_t(b_desc0 >> 32);
+      const uint32_t b_step = p.b_kn ? uint32_t(2048 >> 4) : 2u;
+      uint32_t a_lo = uint32_t(a_desc0), b_lo = uint32_t(b_desc0);
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
@@ -187,27 +197,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = stages_addr + stage * L::kStageBytes;
-          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
-          // b as (N, K): K-major like a, 32 bytes of K per instruction inside the swizzle span. b as (K, N): an
-          // MN-major operand, 64-column blocks 8192 bytes apart, 8-row K groups 1024 bytes apart, 16 K rows per
-          // instruction = 2048 bytes.
-          const uint64_t b_desc = p.b_kn ? umma_desc_mnmajor_sw128(a_addr + L::kABytes, 8192, 1024)
-                                         : umma_desc_kmajor_sw128(a_addr + L::kABytes);
-          const uint64_t b_step = p.b_kn ? uint64_t(2048 >> 4) : 2;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            umma_ss<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_desc + 2 * ks, b_desc + b_step * ks, idesc,
-                                                (kb > 0 || ks > 0) ? 1u : 0u);
+            umma_ss_halves<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_lo + 2 * ks, a_hi, b_lo + b_step * ks, b_hi, idesc,
+                                                       (kb > 0 || ks > 0) ? 1u : 0u);
           }
           if constexpr (CTA_GROUP == 1) {
             umma_commit(empty_bar + 8 * stage);
           } else {
             umma_commit_pair(empty_bar + 8 * stage, 0x3);
           }
+          a_lo += L::kStageBytes >> 4;
+          b_lo += L::kStageBytes >> 4;
           if (++stage == L::kStages) {
             stage = 0;
             phase ^= 1u;
+            a_lo = uint32_t(a_desc0);
+            b_lo = uint32_t(b_desc0);
           }
         }
         if (!ok) break;

@@ -338,36 +338,36 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
   }
 }
 
-// The same instruction with the two descriptors given as 32-bit halves. Both operands of the kernels here share the
-// upper descriptor word (same swizzle, strides and version), and only the 14-bit start-address field in the lower
-// word moves from stage to stage, so the issuing thread — a single thread whose every instruction waits for the
-// previous one — adds one 32-bit constant per operand instead of doing 64-bit descriptor arithmetic.
+// The same instruction with the two descriptors given as 32-bit halves. The upper word of a descriptor (swizzle,
+// strides, version) never changes inside a kernel and only the 14-bit start-address field of the lower word moves from
+// stage to stage, so the issuing thread — a single thread whose every instruction waits for the previous one — adds
+// one 32-bit constant per operand instead of doing 64-bit descriptor arithmetic.
 template <int CTA_GROUP, bool KIND_F8>
-__device__ __forceinline__ void umma_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+__device__ __forceinline__ void umma_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                                uint32_t idesc, uint32_t accumulate) {
   if constexpr (CTA_GROUP == 1 && !KIND_F8) {
     asm volatile(
-        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n"
-        " mov.b64 db, {%2, %3};\n tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else if constexpr (CTA_GROUP == 2 && !KIND_F8) {
     asm volatile(
-        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n"
-        " mov.b64 db, {%2, %3};\n tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else if constexpr (CTA_GROUP == 1 && KIND_F8) {
     asm volatile(
-        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n"
-        " mov.b64 db, {%2, %3};\n tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
-        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n"
-        " mov.b64 db, {%2, %3};\n tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
