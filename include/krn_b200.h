@@ -76,6 +76,26 @@ int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void
 int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
                      int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
+/* epilogue flags of krn_b200_matmul: KRN_B200_EPILOGUE_BIAS may be or-ed with one activation */
+#define KRN_B200_EPILOGUE_NONE 0
+#define KRN_B200_EPILOGUE_BIAS 1
+#define KRN_B200_EPILOGUE_RELU 2
+#define KRN_B200_EPILOGUE_GELU 4
+#define KRN_B200_EPILOGUE_SILU 6
+
+/* out = activation(A * B + bias): the product with the reference's fused epilogues — the statements of its
+ * `matmul_epilogue` kernel (src/krn/lib/lib_kernels.py:30-48) behind `lib.matmul(a, b, epilogue=, bias=)`
+ * (src/krn/lib/lib.py:580-615), applied to the f32 accumulator in the kernel's epilogue before the one rounding to the
+ * output type. relu `x < 0 ? 0 : x`, gelu `0.5 x (1 + erf(x / sqrt 2))`, silu `x / (1 + exp(-x))`
+ * (src/krn/compiler/emit.py:110-114).
+ *   b_kn      0: b is (N, K) (the operand of b.transpose()); 1: b is (K, N), the layout lib.matmul takes
+ *   epilogue  KRN_B200_EPILOGUE_* flags
+ *   bias      vector of N elements of the OUTPUT type (`Operands.bias`, src/krn/lib/lib.py:155-163); read only when
+ *             the BIAS flag is set
+ * Everything else as krn_b200_gemm_tn. With K == 0 the result is activation(bias). */
+int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, const void* a, const void* b, const void* bias,
+                    void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
 /* The same product sharded by output columns over the GPUs of one node, with the all-gather of the output
  * columns done by the kernel itself: rank `rank` of `ranks` multiplies A[M,K] by ITS rows of B (b: [n_local, K])
  * and its epilogue stores the column block [rank * n_local, (rank + 1) * n_local) into EVERY rank's C —

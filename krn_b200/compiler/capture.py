@@ -5,7 +5,8 @@ The reference does the same in one pass over the AST (src/krn/compiler/source.py
 src/krn/compiler/capture.py:427-457); this capture covers what the tile matrix product and the flash-attention
 pattern are written with: `block.tile`, `block.index`, `zeros`, `pipelined`/`range` loops, tensor slicing with
 capture-time extents (src/krn/compiler/capture.py:925-997), `@`, `.transpose()`, `.to()`, elementwise arithmetic,
-`exp2`, row reductions, `where`, `arange`, `maximum`, static `if` on configuration constants, tile stores.
+`exp2`, `.relu()` / `.gelu()` / `.silu()`, row reductions, `where`, `arange`, `maximum`, static `if` on configuration
+constants, tile stores.
 Anything else is refused with a `CaptureError` at the user's line."""
 
 from __future__ import annotations
@@ -89,8 +90,10 @@ def _difference(stop: Any, start: Any) -> int | None:
 
 
 def _broadcast(a: tuple[int, ...], b: tuple[int, ...]) -> tuple[int, ...] | None:
-    if len(a) != len(b):
-        return None
+    """numpy's rule: shapes align at the last axis, missing leading axes count as 1 (`acc += bias[cols]` adds a row
+    vector to every row of the accumulator, src/krn/lib/lib_kernels.py:40-41)."""
+    rank = max(len(a), len(b))
+    a, b = (1,) * (rank - len(a)) + tuple(a), (1,) * (rank - len(b)) + tuple(b)
     out = []
     for x, y in zip(a, b):
         if x == y or y == 1:
@@ -546,6 +549,10 @@ class Builder:
                 raise self.error(node, f".{name}(other) takes one operand")
             return self.math(name, [tile, args[0]], node)
         if name in ("exp2", "exp"):
+            return self.math(name, [tile], node)
+        if name in ("relu", "gelu", "silu"):  # the tile activations (src/krn/frontend/_ops.py:185-205)
+            if args or keywords:
+                raise self.error(node, f".{name}() takes no operands")
             return self.math(name, [tile], node)
         if name in ("max", "sum", "min"):
             return self.reduce(name, tile, args, keywords, node)

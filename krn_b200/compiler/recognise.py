@@ -5,8 +5,9 @@ generator, so a kernel either IS one of the contractions the library implements 
 launched ("never ignore it silently", the reference's refusal policy, AGENTS.md:17). Two patterns:
 
 * tile matrix product — `acc = zeros(f32, bm, bn)`, one K loop of `acc += a[rows, ks] @ b[ks, cols]`
-  (examples/04_libraries/01_gemm_tiles.py:35-40) or of `acc += a[rows, ks] @ b[cols, ks].transpose()`, then
-  `c[rows, cols] = acc.to(T)`;
+  (examples/04_libraries/01_gemm_tiles.py:35-40) or of `acc += a[rows, ks] @ b[cols, ks].transpose()`, optionally the
+  library epilogue `acc += bias[cols].to(f32)` and one of `acc = acc.relu()` / `.gelu()` / `.silu()`
+  (src/krn/lib/lib_kernels.py:30-48), then `c[rows, cols] = acc.to(T)`;
 * flash attention — the statement sequence of examples/04_libraries/08_flash_attention.py:44-59, optionally with a
   leading batch axis and grouped kv heads (`k[head // g, ...]`)."""
 
@@ -32,6 +33,8 @@ class GemmPlan:
     output: Dtype
     tile: tuple[int, int, int]
     transposed_b: bool = True
+    bias: str | None = None        # vector added to every row of the accumulator before the store
+    activation: str | None = None  # "relu", "gelu" or "silu", applied after the bias
 
 
 @dataclass(frozen=True)
@@ -70,11 +73,36 @@ def _loop_slice(e: ir.Expr, loop: ir.For) -> bool:
     return isinstance(e, ir.SliceExpr) and e.start == ir.LoopVar(loop.var) and e.extent == loop.step
 
 
+def _epilogue(kernel: ir.Kernel, acc: ir.Var, statements: list[ir.Stmt], bn: int) -> tuple[str | None, str | None] | None:
+    """(bias tensor, activation) of the statements between the K loop and the store — `acc += bias[cols].to(f32)` and
+    `acc = acc.relu()` / `.gelu()` / `.silu()` (src/krn/lib/lib_kernels.py:40-47) — or None when they are something else."""
+    bias = activation = None
+    for s in statements:
+        if not (isinstance(s, ir.Assign) and s.var == acc and isinstance(s.value, ir.Math)):
+            return None
+        fn, operands = s.value.fn, s.value.operands
+        if fn == "add" and len(operands) == 2 and operands[0] == acc and bias is None and activation is None:
+            vector = operands[1].operand if isinstance(operands[1], ir.Cast) else operands[1]
+            if not (isinstance(vector, ir.TileLoad) and len(vector.index) == 1 and _block_tile(vector.index[0], "x") == bn):
+                return None
+            bias = vector.tensor
+        elif fn in ("relu", "gelu", "silu") and operands == (acc,):
+            if activation is not None:
+                raise refuse(kernel, f"{activation} followed by {fn}: the library epilogue applies one activation",
+                             "keep one of relu, gelu, silu (the reference's Epilogue values name one each)", span=s.span)
+            activation = fn
+        else:
+            return None
+    return bias, activation
+
+
 def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
     body = kernel.body
-    if len(body) != 3 or not isinstance(body[0], ir.Assign) or not isinstance(body[1], ir.For) \
-            or not isinstance(body[2], ir.TileStore):
+    if len(body) < 3 or not isinstance(body[0], ir.Assign) or not isinstance(body[1], ir.For) \
+            or not isinstance(body[-1], ir.TileStore):
         return None
+    tail = list(body[2:-1])
+    body = (body[0], body[1], body[-1])
     init, loop, store = body
     if not (isinstance(init.value, ir.Zeros) and init.value.value == 0.0 and init.value.dtype == f32
             and len(init.value.shape) == 2):
@@ -117,7 +145,15 @@ def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
     output = kernel.tensor(store.tensor).dtype
     if output.name not in ("bf16", "f16", "f32"):
         raise refuse(kernel, f"{output} outputs are not supported", "store bf16, f16 or f32", span=store.span)
-    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step), transposed_b)
+    epilogue = _epilogue(kernel, init.var, tail, bn)
+    if epilogue is None:
+        return None
+    bias, activation = epilogue
+    if bias is not None and kernel.tensor(bias).dtype != output:
+        raise refuse(kernel, f"a {kernel.tensor(bias).dtype} bias on a {output} result: the library epilogue reads the "
+                             "bias in the type of the result", "declare bias and out with one element type",
+                     span=store.span)
+    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step), transposed_b, bias, activation)
 
 
 def _head_index(e: ir.Expr) -> int | None:

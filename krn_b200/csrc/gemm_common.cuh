@@ -1,6 +1,8 @@
 // Pieces shared by the tile-product kernels: the problem record and the persistent tile order.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "host.cuh"
 
 namespace krnb {
@@ -10,6 +12,38 @@ struct Problem {
   int tiles_m, tiles_n;
   int b_kn;  // 0: b is (N, K), the operand of `b.transpose()`; 1: b is (K, N), the operand of a plain `a @ b`
 };
+
+// What happens to the f32 accumulator between the last K step and the rounding to the output type:
+// `out = activation(acc + bias[column])`, the statements of the reference's `matmul_epilogue` kernel
+// (src/krn/lib/lib_kernels.py:30-48). flags = KRN_B200_EPILOGUE_* of include/krn_b200.h: bit 0 adds the bias (a
+// vector of the OUTPUT type, as `Operands.bias`, src/krn/lib/lib.py:155-163), bits 1-2 pick the activation.
+struct EpilogueSpec {
+  const void* bias;
+  int flags;
+};
+constexpr int kEpilogueBias = 1;
+constexpr int kActivationRelu = 1, kActivationGelu = 2, kActivationSilu = 3;
+
+// The reference's element functions in f32 (src/krn/compiler/emit.py:110-114): relu `x < 0 ? 0 : x`, gelu
+// `0.5 x (1 + erf(x / sqrt 2))` (the exact Gaussian form), silu `x / (1 + exp(-x))`.
+__device__ __forceinline__ float apply_activation(float x, int activation) {
+  if (activation == kActivationRelu) return x < 0.f ? 0.f : x;
+  if (activation == kActivationGelu) return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+  if (activation == kActivationSilu) return x / (1.f + expf(-x));
+  return x;
+}
+
+// Element `index` of a bias vector stored in the output type (f32 words, or 16-bit bf16 / f16 words).
+template <typename OutT, bool OUT_BF16>
+__device__ __forceinline__ float load_bias(const void* bias, long long index) {
+  if constexpr (sizeof(OutT) == 4) {
+    return __ldg(static_cast<const float*>(bias) + index);
+  } else {
+    const uint16_t w = __ldg(static_cast<const uint16_t*>(bias) + index);
+    if constexpr (OUT_BF16) return __uint_as_float(uint32_t(w) << 16);
+    return __half2float(__ushort_as_half(w));
+  }
+}
 
 // Tile order: bands of 8 tile rows walked column by column, so that the tiles in flight at any time
 // share a few A row-panels and B column-panels in L2.

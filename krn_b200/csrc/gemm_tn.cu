@@ -59,10 +59,27 @@ struct Destinations {
 
 enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
 
+// `values[i]` is this thread's accumulator for output column `col + i` (i < 32): add the bias of that column and apply
+// the activation, in f32, before the rounding. Lane l fetches the bias of column col + l once; the 32 columns are then
+// read from the lanes by shuffle (every lane needs all 32).
+template <typename OutT, bool OUT_BF16>
+__device__ __forceinline__ void fused_epilogue(uint32_t (&values)[32], const EpilogueSpec& epilogue, int col, int n,
+                                               uint32_t lane) {
+  const int activation = epilogue.flags >> 1;
+  float mine = 0.f;
+  if ((epilogue.flags & kEpilogueBias) && col + int(lane) < n) mine = load_bias<OutT, OUT_BF16>(epilogue.bias, col + int(lane));
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float x = __uint_as_float(values[i]) + __shfl_sync(0xffffffffu, mine, i);
+    values[i] = __float_as_uint(apply_activation(x, activation));
+  }
+}
+
 template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ Destinations dst, Problem p, uint32_t ab_format, DeviceStatus* status) {
+               const __grid_constant__ Destinations dst, Problem p, EpilogueSpec epilogue, uint32_t ab_format,
+               DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kBK = kRowBytes / ELEM_BYTES;                 // K elements per stage
   constexpr int kChunkCols = kRowBytes / int(sizeof(OutT));   // output columns per 128-byte store row
@@ -254,11 +271,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if constexpr (sizeof(OutT) == 4) {
           tmem_ld_32x32(t_row + chunk * kChunkCols, packed);
           tmem_ld_wait(packed);
+          if (epilogue.flags != 0) fused_epilogue<OutT, OUT_BF16>(packed, epilogue, col, p.n, lane);
         } else {
           uint32_t lo[32], hi[32];
           tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
           tmem_ld_wait(lo, hi);
+          if (epilogue.flags != 0) {
+            fused_epilogue<OutT, OUT_BF16>(lo, epilogue, col, p.n, lane);
+            fused_epilogue<OutT, OUT_BF16>(hi, epilogue, col + 32, p.n, lane);
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             if constexpr (OUT_BF16) {
@@ -326,7 +348,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
-           uint32_t fmt, cudaStream_t stream) {
+           EpilogueSpec epilogue, uint32_t fmt, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_tn_kernel<CTA_GROUP, 2, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
@@ -345,7 +367,7 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, fmt, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, epilogue, fmt, ctx->status_dev));
   return KRN_B200_OK;
 }
 
@@ -361,7 +383,8 @@ __device__ __forceinline__ float load_16bit(const uint16_t* p, bool bf16) {
 
 __global__ void __launch_bounds__(256)
 gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, void* __restrict__ c, int m,
-                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type, bool b_kn) {
+                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type, bool b_kn,
+                         EpilogueSpec epilogue) {
   __shared__ float as[16][65], bs[16][65];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
@@ -388,12 +411,21 @@ gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restr
       const int r = row0 + ty * 4 + i, col = col0 + tx * 4 + j;
       if (r >= m || col >= n) continue;
       const long long at = (long long)r * ldc + col;
+      float value = acc[i][j];
+      if (epilogue.flags != 0) {
+        if (epilogue.flags & kEpilogueBias) {
+          value += c_type == KRN_B200_F32    ? load_bias<float, false>(epilogue.bias, col)
+                   : c_type == KRN_B200_BF16 ? load_bias<uint16_t, true>(epilogue.bias, col)
+                                             : load_bias<uint16_t, false>(epilogue.bias, col);
+        }
+        value = apply_activation(value, epilogue.flags >> 1);
+      }
       if (c_type == KRN_B200_F32) {
-        static_cast<float*>(c)[at] = acc[i][j];
+        static_cast<float*>(c)[at] = value;
       } else if (c_type == KRN_B200_BF16) {
-        static_cast<uint16_t*>(c)[at] = uint16_t(pack_bf16x2(acc[i][j], 0.f) & 0xffffu);
+        static_cast<uint16_t*>(c)[at] = uint16_t(pack_bf16x2(value, 0.f) & 0xffffu);
       } else {
-        static_cast<uint16_t*>(c)[at] = uint16_t(pack_f16x2(acc[i][j], 0.f) & 0xffffu);
+        static_cast<uint16_t*>(c)[at] = uint16_t(pack_f16x2(value, 0.f) & 0xffffu);
       }
     }
 }
@@ -427,7 +459,7 @@ int gemm_pair_mode(int64_t m) {
 static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type, const void* a, const void* b,
                          void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m,
                          int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream,
-                         bool b_kn = false) {
+                         bool b_kn = false, krnb::EpilogueSpec epilogue = {nullptr, 0}) {
   using namespace krnb;
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
   Problem p;
@@ -474,18 +506,19 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
   }
   const uint32_t fmt = ab_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
   if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, fmt, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, fmt, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
   }
-  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, fmt, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, fmt, stream);
-  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, fmt, stream);
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
 }
 
 // Argument checks, the K == 0 and unaligned cases and the launch, shared by the two layouts of b.
 static int product(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                   int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle, bool b_kn) {
+                   int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle, bool b_kn,
+                   krnb::EpilogueSpec epilogue = {nullptr, 0}) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
@@ -514,30 +547,32 @@ static int product(int ab_type, int c_type, const void* a, const void* b, void* 
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
 
-  if (k == 0) {
+  if (k == 0 && epilogue.flags == 0) {
     // the zero accumulator is stored untouched (src/krn/compiler/emit.py:739-755)
     zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(static_cast<uint8_t*>(c), n * c_bytes, ldc * c_bytes, m);
     KRNB_CUDA(cudaGetLastError());
     return KRN_B200_OK;
   }
-  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 ||
+  if (k == 0 || !aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 ||
       (ldc * c_bytes) % 16 != 0) {
-    // not describable to TMA: the plain tiled kernel (element-aligned addresses are all it needs)
-    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 2 != 0 ||
+    // not describable to TMA (or an epilogue over an empty sum): the plain tiled kernel, which needs element-aligned
+    // addresses only and never touches a or b when K is 0
+    if ((k > 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 2 != 0) ||
         reinterpret_cast<uintptr_t>(c) % c_bytes != 0) {
       return fail(KRN_B200_ERR_INVALID_ARGUMENT, "tensor addresses must be aligned to their element size");
     }
     const dim3 grid(unsigned((n + 63) / 64), unsigned((m + 63) / 64), 1);
     gemm_tn_unaligned_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b),
                                                        c, int(m), int(n), int(k), lda, ldb, ldc,
-                                                       ab_type == KRN_B200_BF16, c_type, b_kn);
+                                                       ab_type == KRN_B200_BF16, c_type, b_kn, epilogue);
     KRNB_CUDA(cudaGetLastError());
     return KRN_B200_OK;
   }
 
   const int group = gemm_pair_mode(m);
   void* destinations[1] = {c};
-  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream, b_kn);
+  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream, b_kn,
+                       epilogue);
 }
 
 extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
@@ -548,6 +583,25 @@ extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const vo
 extern "C" int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
   return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, true);
+}
+
+extern "C" int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, const void* a, const void* b,
+                               const void* bias, void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                               int64_t ldc, void* stream_handle) {
+  using namespace krnb;
+  const int activation = epilogue >> 1;
+  if (epilogue < 0 || activation > kActivationSilu) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "epilogue flags %d: bit 0 adds the bias, bits 1-2 pick relu (1), gelu "
+                "(2) or silu (3)", epilogue);
+  }
+  if ((epilogue & kEpilogueBias) && bias == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the epilogue adds a bias but the bias address is null");
+  }
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  if ((epilogue & kEpilogueBias) && reinterpret_cast<uintptr_t>(bias) % c_bytes != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the bias vector must be aligned to the output element size");
+  }
+  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, b_kn != 0, EpilogueSpec{bias, epilogue});
 }
 
 extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank,

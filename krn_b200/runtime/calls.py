@@ -70,6 +70,25 @@ def gemm_nn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
     native.check(status, "tile matrix product")
 
 
+def matmul(a: Any, b: Any, c: Any, *, b_kn: bool = True, epilogue: int = 0, bias: Any = None, stream: Any = None) -> None:
+    """c = activation(a @ b + bias): `b` is (K, N) when `b_kn` (the layout `lib.matmul` takes) or (N, K) otherwise;
+    `epilogue` holds the KRN_B200_EPILOGUE_* flags (bit 0 bias, bits 1-2 relu / gelu / silu); `bias` is a vector of N
+    elements of c's type."""
+    (m, k) = a.shape
+    kb, n = (b.shape[0], b.shape[1]) if b_kn else (b.shape[1], b.shape[0])
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    if _type_of(a) != _type_of(b):
+        raise TypeError("both operands must have the same element type")
+    if bias is not None and (tuple(bias.shape) != (n,) or _type_of(bias) != _type_of(c)):
+        raise TypeError(f"the bias must be a vector of {n} elements of the output type")
+    status = native.library().krn_b200_matmul(
+        _type_of(a), _type_of(c), int(b_kn), int(epilogue), _pointer(a), _pointer(b),
+        _pointer(bias) if bias is not None else None, _pointer(c), m, n, k, _pitch(a), _pitch(b), _pitch(c),
+        _stream(stream))
+    native.check(status, "tile matrix product with epilogue")
+
+
 def gemm_tn_gather(a: Any, b_local: Any, c_pointers: list[int], rank: int, m: int, n_local: int, ldc: int, c_type: int,
                    stream: Any = None) -> None:
     """This rank's column block of c = a @ b^T, stored by the kernel's epilogue into every rank's full C.

@@ -228,10 +228,18 @@ class B200Launcher(api.Launcher):
         explanation = api.Explanation(
             captured.name, f"tile matrix product c = a @ b{'^T' if plan.transposed_b else ''}, {plan.operand} operands, "
             f"{plan.output} output, declared tile {plan.tile}", launch or needed,
-            f"krn_b200_gemm_{'tn' if plan.transposed_b else 'nn'} (tcgen05, 256x256 CTA-pair tiles)",
+            ("krn_b200_matmul" if plan.bias or plan.activation else
+             f"krn_b200_gemm_{'tn' if plan.transposed_b else 'nn'}") + " (tcgen05, 256x256 CTA-pair tiles)",
             ("the library chooses its own CTA tiling; the declared tile only shapes the inferred geometry",))
-        product = calls.gemm_tn if plan.transposed_b else calls.gemm_nn
-        return Call(lambda stream: product(a, b, c, stream.raw), explanation)
+        if plan.bias is None and plan.activation is None:
+            product = calls.gemm_tn if plan.transposed_b else calls.gemm_nn
+            return Call(lambda stream: product(a, b, c, stream.raw), explanation)
+        bias = _raw(named[plan.bias]) if plan.bias is not None else None
+        flags = (1 if bias is not None else 0) | {None: 0, "relu": 2, "gelu": 4, "silu": 6}[plan.activation]
+        if bias is not None and tuple(bias.shape) != (c.shape[1],):
+            raise ValueError(f"{captured.name}: the bias has {tuple(bias.shape)} elements for {c.shape[1]} columns")
+        return Call(lambda stream: calls.matmul(a, b, c, b_kn=not plan.transposed_b, epilogue=flags, bias=bias,
+                                                stream=stream.raw), explanation)
 
     def _attention(self, captured, plan: AttentionPlan, named, shapes, launch) -> Call:
         q, k, v, o = (_raw(named[n]) for n in (plan.q, plan.k, plan.v, plan.o))

@@ -26,6 +26,7 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
     "krn_b200_device_status": (_int, [ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(ctypes.c_uint)]),
     "krn_b200_gemm_tn": (_int, [_int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_copy_2d": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
+    "krn_b200_matmul": (_int, [_int, _int, _int, _int, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_nn": (_int, [_int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_tn_gather": (_int, [_int, _int, _ptr, _ptr, ctypes.POINTER(_ptr), _int, _int, _i64, _i64, _i64, _i64,
                                        _i64, _i64, _ptr]),

@@ -128,6 +128,28 @@ static inline void store_from_f32(void* base, int type, int64_t index, float val
   }
 }
 
+/* ---- fused epilogue of the library matmul ---------------------------------------------------------------- */
+
+/* The tail of the reference's `matmul_epilogue` kernel (src/krn/lib/lib_kernels.py:40-48) applied to the f32
+ * accumulator `acc` (m x n, what the K loop leaves): `acc += bias[cols].to(f32)` when bit 0 of `flags` is set (the bias
+ * has the output type, src/krn/lib/lib.py:155-163), then relu / gelu / silu (bits 1-2 = 1 / 2 / 3) with the element
+ * functions the C renderer writes for f32 (src/krn/compiler/emit.py:110-114: `x < 0 ? 0 : x`,
+ * `0.5f * x * (1 + erff(x * 0.7071067811865476f))`, `x / (1 + expf(-x))`), then `out = acc.to(out type)`. */
+void krn_oracle_matmul_epilogue(int c_type, const float* acc, const void* bias, void* out, int64_t m, int64_t n,
+                                int flags) {
+  const int activation = flags >> 1;
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      float x = acc[i * n + j];
+      if (flags & 1) x = x + load_as_f32(bias, c_type, j);
+      if (activation == 1) x = x < 0 ? 0 : x;
+      if (activation == 2) x = 0.5f * x * (1 + erff(x * 0.7071067811865476f));
+      if (activation == 3) x = x / (1 + expf(-x));
+      store_from_f32(out, c_type, i * n + j, x);
+    }
+  }
+}
+
 /* ---- tile matrix product, faithful loop structure --------------------------------------------------- */
 
 /* The kernel

@@ -56,7 +56,8 @@ def lib() -> ctypes.CDLL:
         handle.krn_oracle_e4m3_encode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_e4m3_decode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_bf16_round_array.argtypes = [ptr, ptr, i64]
-        for name in ("gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
+        handle.krn_oracle_matmul_epilogue.argtypes = [i32, ptr, ptr, ptr, i64, i64, i32]
+        for name in ("matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
                      "e4m3_encode_array", "e4m3_decode_array", "bf16_round_array"):
             getattr(handle, f"krn_oracle_{name}").restype = None
         _LIB = handle
@@ -139,6 +140,22 @@ def gemm(a: np.ndarray, b: np.ndarray, *, ab_type: int, c_type: int, b_kn: bool 
         _run(_split(m, threads), lambda lo, hi: lib().krn_oracle_gemm_fast(
             ab_type, c_type, int(b_kn), _p(a), _p(b), _p(c), m, n, k, a.shape[1], b.shape[1], n, lo, hi))
     return c
+
+
+EPILOGUE_BIAS, EPILOGUE_RELU, EPILOGUE_GELU, EPILOGUE_SILU = 1, 2, 4, 6
+
+
+def matmul_epilogue(a: np.ndarray, b: np.ndarray, bias: np.ndarray | None, *, ab_type: int, c_type: int, flags: int,
+                    b_kn: bool = True, threads: int = 1) -> np.ndarray:
+    """`activation(a @ b + bias)` as the reference's `matmul_epilogue` kernel computes it
+    (src/krn/lib/lib_kernels.py:30-48): the k-ordered f32 accumulation of `gemm`, the bias (storage words of the
+    output type) and the activation in f32, one rounding to `c_type`. `flags` = EPILOGUE_BIAS | one activation."""
+    acc = gemm(a, b, ab_type=ab_type, c_type=F32, b_kn=b_kn, threads=threads)
+    m, n = acc.shape
+    out = np.zeros((m, n), _NUMPY[c_type])
+    words = np.zeros(n, _NUMPY[c_type]) if bias is None else np.ascontiguousarray(bias, _NUMPY[c_type])
+    lib().krn_oracle_matmul_epilogue(c_type, _p(acc), _p(words), _p(out), m, n, flags)
+    return out
 
 
 def gemm_fp8_blockscaled(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.ndarray, *, c_type: int = BF16,

@@ -1,6 +1,7 @@
 """Kernel sources the front-end tests capture (capture reads source files, so kernels live in a module)."""
 
-from krn_b200 import Const, Matrix, T, Tensor, arange, bf16, block, f16, f32, kernel, pipelined, struct, where, zeros
+from krn_b200 import (Const, Matrix, T, Tensor, Vector, arange, bf16, block, f16, f32, kernel, pipelined, struct, where,
+                      zeros)
 
 
 @struct
@@ -36,6 +37,37 @@ def matmul_nn(t: Tiling, a: Matrix[f16], b: Matrix[f16], c: Matrix[f16]) -> None
     for ks in pipelined(a.shape[1], t.bk):
         acc += a[rows, ks] @ b[ks, cols]
     c[rows, cols] = acc.to(f16)
+
+
+@struct
+class MatmulTiling:
+    """The configuration of the reference's library kernel (src/krn/lib/lib_kernels.py:18-28)."""
+
+    bm: Const[int] = 64
+    bn: Const[int] = 64
+    bk: Const[int] = 32
+    bias: Const[bool] = False
+    relu: Const[bool] = False
+    gelu: Const[bool] = False
+    silu: Const[bool] = False
+
+
+@kernel
+def matmul_epilogue(t: MatmulTiling, a: Matrix[f16], b: Matrix[f16], bias: Vector[f16], out: Matrix[f16]) -> None:
+    """`out = activation(a @ b + bias)`, the statements of src/krn/lib/lib_kernels.py:30-48."""
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk):
+        acc += a[rows, ks] @ b[ks, cols]
+    if t.bias:
+        acc += bias[cols].to(f32)
+    if t.relu:
+        acc = acc.relu()
+    if t.gelu:
+        acc = acc.gelu()
+    if t.silu:
+        acc = acc.silu()
+    out[rows, cols] = acc.to(f16)
 
 
 @kernel

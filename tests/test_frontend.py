@@ -66,6 +66,37 @@ def test_recognise_gemm_forms() -> None:
     assert "tile_kernels.py" in text and "^" in text  # compiler-style location with a caret
 
 
+def test_recognise_library_epilogues() -> None:
+    """The reference's `matmul_epilogue` kernel (src/krn/lib/lib_kernels.py:30-48) under each flag set."""
+    tile = (64, 64, 32)
+    plan = recognise(capture(K.matmul_epilogue.fn, K.MatmulTiling()))
+    assert plan == GemmPlan("a", "b", "out", krn.f16, krn.f16, tile, False)
+    plan = recognise(capture(K.matmul_epilogue.fn, K.MatmulTiling(bias=True, gelu=True)))
+    assert plan == GemmPlan("a", "b", "out", krn.f16, krn.f16, tile, False, "bias", "gelu")
+    assert recognise(capture(K.matmul_epilogue.fn, K.MatmulTiling(silu=True))).activation == "silu"
+    with pytest.raises(TargetError, match="relu followed by gelu"):
+        recognise(capture(K.matmul_epilogue.fn, K.MatmulTiling(relu=True, gelu=True)))
+
+
+def test_library_candidate_protocol() -> None:
+    """Names, refusals and flags of the one matmul candidate (protocol of src/krn/lib/lib.py:201-235)."""
+    from krn_b200 import lib
+
+    candidate = lib.CANDIDATES[0]
+    assert (candidate.name, candidate.op, candidate.origin) == ("b200", lib.Op.MATMUL, lib.Origin.OURS)
+    assert [e.value for e in lib.Epilogue] == ["none", "bias", "relu", "gelu", "bias_relu", "bias_gelu", "silu"]
+    assert lib.FLAGS[lib.Epilogue.BIAS_GELU] == 1 | 4 and lib.FLAGS[lib.Epilogue.SILU] == 6
+    problem = lib.Problem(lib.Op.MATMUL, (krn.bf16, krn.bf16, krn.f32), (8, 8, 8), lib.LibOptions())
+    assert candidate.refusal(problem, "sm_100a") is None
+    mixed = lib.Problem(lib.Op.MATMUL, (krn.bf16, krn.f16, krn.f32), (8, 8, 8), lib.LibOptions())
+    assert "got bf16 @ f16" in candidate.refusal(mixed, "sm_100a")
+    carved = lib.Problem(lib.Op.MATMUL, (krn.f16, krn.f16, krn.f16), (8, 8, 8), lib.LibOptions(sm_count=64))
+    assert "sm_count" in candidate.refusal(carved, "sm_100a")
+    relaxed = lib.Problem(lib.Op.MATMUL, (krn.f16, krn.f16, krn.f16), (8, 8, 8), lib.LibOptions(), precision=lib.Compute.TF32)
+    assert "tf32" in candidate.refusal(relaxed, "sm_100a")
+    assert lib.product_type(krn.f16, krn.f16) == krn.f16 and lib.product_type(krn.f16, krn.bf16) == krn.f32
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_recognise_flash_attention_example(causal) -> None:
     captured = capture(K.flash_attention.fn, K.Heads(causal=causal, d=128))

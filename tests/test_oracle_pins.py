@@ -244,3 +244,24 @@ def test_paged_decode_definition_is_consistent() -> None:
             p = np.exp(s - s.max())
             want = (p / p.sum()) @ vv[:, h // 2]
             np.testing.assert_allclose(out[b, h], want, atol=2e-2, rtol=2e-2)
+
+
+def test_matmul_epilogue_restatement_matches_the_reference_element_functions() -> None:
+    """f32 end to end, against numpy written from the emulator's definitions (src/krn/emulator/emulate.py:376-385:
+    relu `maximum(x, 0)`, silu `x / (1 + exp(-x))`, gelu `0.5 x (1 + erf(x * 0.7071067811865476))`)."""
+    import math
+
+    rng = np.random.default_rng(12)
+    a, b = rng.uniform(-1, 1, (9, 40)).astype(np.float32), rng.uniform(-1, 1, (40, 11)).astype(np.float32)
+    bias = rng.uniform(-2, 2, 11).astype(np.float32)
+    x = (a.astype(np.float64) @ b.astype(np.float64))
+    erf = np.vectorize(math.erf)
+    for flags, fn in ((0, lambda v: v), (o.EPILOGUE_BIAS, lambda v: v + bias), (o.EPILOGUE_RELU, lambda v: np.maximum(v, 0)),
+                      (o.EPILOGUE_BIAS | o.EPILOGUE_GELU, lambda v: 0.5 * (v + bias) * (1 + erf((v + bias) * 0.7071067811865476))),
+                      (o.EPILOGUE_SILU, lambda v: v / (1 + np.exp(-v)))):
+        got = o.matmul_epilogue(a, b, bias, ab_type=o.F32, c_type=o.F32, flags=flags)
+        np.testing.assert_allclose(got, fn(x), rtol=2e-5, atol=2e-6)
+    # a bf16 result is the f32 value rounded once
+    got = o.matmul_epilogue(a, b, o.bf16_words(bias), ab_type=o.F32, c_type=o.BF16, flags=o.EPILOGUE_BIAS)
+    want = o.bf16_words((o.gemm(a, b, ab_type=o.F32, c_type=o.F32, b_kn=True) + o.bf16_values(o.bf16_words(bias))).astype(np.float32))
+    np.testing.assert_array_equal(got, want)
