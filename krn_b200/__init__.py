@@ -15,15 +15,18 @@ from krn_b200.frontend.device_functions import (UNIFORM, PingPong, Space, Unifor
                                                 full, maximum, minimum, pipelined, where, zeros)
 from krn_b200.frontend.geometry import Blocks, Items, Tiles
 from krn_b200.frontend.kernel import Kernel, kernel
+from krn_b200.frontend.variants import AmbiguousVariant, Family, family
 from krn_b200.frontend.records import AUTO, Const, struct
 from krn_b200.frontend.types import (QMatrix, QTile, T, Matrix, Tensor, Tile, Vector, bf16, f8e4m3fn, f8e5m2, f16, f32,
                                      f64, i32, i64, u8, u32)
 from krn_b200.runtime.settings import config, configure
+from krn_b200.targets import Feature
 
 __all__ = [
-    "AUTO", "Blocks", "CUDAError", "CaptureError", "Const", "Items", "Kernel", "LaunchError", "Matrix",
+    "AUTO", "AmbiguousVariant", "Blocks", "CUDAError", "CaptureError", "Const", "Family", "Feature", "Items", "Kernel",
+    "LaunchError", "Matrix",
     "PerformanceWarning", "PingPong", "PrecisionWarning", "QMatrix", "QTile", "Space", "T", "TargetError", "Tensor",
     "Tile", "Tiles", "UNIFORM", "Uniform", "Vector", "WarpSpecialized", "arange", "bf16", "block", "chunks", "config",
-    "configure", "errors", "f16", "f32", "f64", "f8e4m3fn", "f8e5m2", "formats", "full", "host", "hw", "i32", "i64",
+    "configure", "errors", "f16", "family", "f32", "f64", "f8e4m3fn", "f8e5m2", "formats", "full", "host", "hw", "i32", "i64",
     "kernel", "maximum", "minimum", "pipelined", "struct", "targets", "u32", "u8", "where", "zeros",
 ]

@@ -494,6 +494,11 @@ class Builder:
                     ir.SliceExpr(_fold("*", ir.BlockIndex("x"), args[1]), args[1]))
         if callee is df.block.index:
             return _Index3()
+        if callee in (df.WarpSpecialized, df.PingPong, df.Uniform):
+            # a schedule is an intent attached to `pipelined(..., schedule=)`: built here, carried on the loop
+            if not all(isinstance(v, int) for v in [*args, *keywords.values()]):
+                raise self.error(e, "a schedule is built from capture-time integers")
+            return callee(*args, **keywords)
         if callee is df.zeros or callee is df.full:
             dtype = args[0]
             value, extent = (0.0, args[1:]) if callee is df.zeros else (float(args[1]), args[2:])

@@ -19,6 +19,7 @@ TARGETS = ("sm_100a",)
 class Run:
     target: str = "sm_100a"
     graphs: bool = True
+    variants: tuple[tuple[str, str], ...] = ()  # family name -> pinned variant ("portable" for the portable kernel)
 
 
 @dataclass(frozen=True)
@@ -75,13 +76,17 @@ def _apply(settings: Settings, dotted: str, value: Any) -> Settings:
         if not isinstance(value, bool):
             raise SettingError(dotted, str(value), "a bool")
         return replace(settings, run=replace(settings.run, graphs=value))
+    if group == "run" and name == "variants":
+        if not isinstance(value, dict) or not all(isinstance(k, str) and isinstance(v, str) for k, v in value.items()):
+            raise SettingError(dotted, str(value), "a mapping of family name to variant name")
+        return replace(settings, run=replace(settings.run, variants=tuple(value.items())))
     if group == "run" and name == "config":
         if not isinstance(value, dict):
             raise SettingError(dotted, str(value), "a mapping of kernel name to configuration")
         return replace(settings, configurations=tuple(value.items()))
     if group == "cache" and name == "dir":
         return replace(settings, cache=Cache(str(value)))
-    raise SettingError(dotted, str(value), "a setting this path reads (run.target, run.graphs, run.config, cache.dir)")
+    raise SettingError(dotted, str(value), "a setting this path reads (run.target, run.graphs, run.config, run.variants, cache.dir)")
 
 
 class configure:

@@ -1,7 +1,7 @@
 """Kernel sources the front-end tests capture (capture reads source files, so kernels live in a module)."""
 
-from krn_b200 import (Const, Matrix, T, Tensor, Vector, arange, bf16, block, f16, f32, kernel, pipelined, struct, where,
-                      zeros)
+from krn_b200 import (Const, Feature, Matrix, PingPong, Space, T, Tensor, Vector, WarpSpecialized, arange, bf16, block, f16,
+                      f32, family, kernel, pipelined, struct, targets, where, zeros)
 
 
 @struct
@@ -175,4 +175,53 @@ def fp8_needs_direct_loads(a: Matrix[T.f8e4m3fn], b: Matrix[T.f8e4m3fn], c: Matr
     acc = zeros(f32, 32, 32)
     for ks in pipelined(a.shape[1], 32):
         acc += a[rows, ks] @ (b[cols, ks] + b[cols, ks]).transpose()
+    c[rows, cols] = acc
+
+
+# ---- a kernel family: one contract, the variant chosen by what the target can do ------------------------------------
+# (the shape of examples/04_libraries/03_gemm_variants.py:43-90)
+
+
+@struct
+class FamilyTiling:
+    bm: Const[int] = 128
+    bn: Const[int] = 128
+    bk: Const[int] = 64
+
+
+@family
+def gemm(t: FamilyTiling, a: Matrix[T.f16], b: Matrix[T.f16], c: Matrix[T.f32]) -> None:
+    """Portable: C = A @ B on whatever matrix unit the target has."""
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(T.f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk):
+        acc += a[rows, ks] @ b[ks, cols]
+    c[rows, cols] = acc
+
+
+@gemm.variant(targets.Nvidia, requires={Feature.TENSOR_MEMORY})
+def gemm_tensor_memory(t: FamilyTiling, a: Matrix[T.f16], b: Matrix[T.f16], c: Matrix[T.f32]) -> None:
+    """The accumulator lives in tensor memory; one producer, one consumer."""
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(T.f32, t.bm, t.bn, space=Space.TENSOR_MEMORY)
+    for ks in pipelined(a.shape[1], t.bk, schedule=WarpSpecialized(producers=1, consumers=1)):
+        acc += a[rows, ks] @ b[ks, cols]
+    c[rows, cols] = acc
+
+
+@gemm.variant(arch={"sm_90a"})
+def gemm_hopper(t: FamilyTiling, a: Matrix[T.f16], b: Matrix[T.f16], c: Matrix[T.f32]) -> None:
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(T.f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk, schedule=WarpSpecialized(producers=1, consumers=2)):
+        acc += a[rows, ks] @ b[ks, cols]
+    c[rows, cols] = acc
+
+
+@gemm.variant(targets.AMD, requires={Feature.ASYNC_COPY})
+def gemm_amd(t: FamilyTiling, a: Matrix[T.f16], b: Matrix[T.f16], c: Matrix[T.f32]) -> None:
+    rows, cols = block.tile(t.bm, t.bn)
+    acc = zeros(T.f32, t.bm, t.bn)
+    for ks in pipelined(a.shape[1], t.bk, stages=2, schedule=PingPong()):
+        acc += a[rows, ks] @ b[ks, cols]
     c[rows, cols] = acc

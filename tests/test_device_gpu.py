@@ -64,6 +64,23 @@ def test_reference_example_form_with_row_major_b(device) -> None:
         np.testing.assert_array_equal(got, c2.to_host().view(np.uint16))
 
 
+def test_family_launches_the_tensor_memory_variant(device) -> None:
+    """Calling a family runs the variant selected for the current device (src/krn/frontend/variants.py:114-126)."""
+    rng = np.random.default_rng(4)
+    m, n, k = 200, 136, 72
+    a16, b16 = rng.uniform(-1, 1, (m, k)).astype(np.float16), rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    a, b = device.to_device(a16), device.to_device(b16)
+    c1, c2 = device.empty(krn.f32, m, n), device.empty(krn.f32, m, n)
+    assert K.gemm.select(device.target).name == "gemm_tensor_memory"
+    assert "krn_b200_gemm_nn" in str(K.gemm.explain(a, b, c1))
+    K.gemm(a, b, c1)
+    K.gemm[K.FamilyTiling(bm=64, bn=64, bk=32)](a, b, c2)
+    device.default_stream.record().wait(TIMEOUT)
+    exact = a16.astype(np.float64) @ b16.astype(np.float64)
+    assert np.all(np.abs(c1.to_host() - exact) <= o.forward_error_bound(a16, b16, k))
+    np.testing.assert_array_equal(c1.to_host(), c2.to_host())
+
+
 def test_range_loop_f16_f32_and_explain(device) -> None:
     rng = np.random.default_rng(2)
     a16, b16 = rng.uniform(-1, 1, (130, 104)).astype(np.float16), rng.uniform(-1, 1, (72, 104)).astype(np.float16)

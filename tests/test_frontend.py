@@ -78,6 +78,44 @@ def test_recognise_library_epilogues() -> None:
         recognise(capture(K.matmul_epilogue.fn, K.MatmulTiling(relu=True, gelu=True)))
 
 
+def test_family_selection_audit_and_pinning() -> None:
+    """Most specific matching rule wins, ties raise, `run.variants` pins (the reference's family rules,
+    src/krn/frontend/variants.py:47-112, on the family of examples/04_libraries/03_gemm_variants.py)."""
+    from krn_b200 import AmbiguousVariant, Feature, targets
+
+    F = Feature
+    b200 = targets.Target.of("sm_100a")
+    hopper = targets.described(targets.Nvidia, "sm_90a", {F.TENSOR_CORE, F.ASYNC_COPY, F.BULK_COPY, F.ASYNC_MMA, F.CLUSTERS})
+    ampere = targets.described(targets.Nvidia, "sm_80", {F.TENSOR_CORE, F.ASYNC_COPY})
+    mi300 = targets.described(targets.AMD, "gfx942", {F.TENSOR_CORE, F.ASYNC_COPY})
+    cpu = targets.described(targets.CPU, "x86_64", set())
+    assert K.gemm.audit([b200, hopper, ampere, mi300, cpu]) == {
+        "sm_100a": "gemm_tensor_memory", "sm_90a": "gemm_hopper", "sm_80": "portable", "gfx942": "gemm_amd",
+        "x86_64": "portable"}
+    selection = K.gemm.select(b200)
+    assert selection.kernel is K.gemm_tensor_memory and "most specific" in selection.reason
+    assert K.gemm.select(cpu).reason == "no variant applies to x86_64"
+    # the selected variant is the tile product with row-major b, its space= and schedule= intents accepted
+    plan = recognise(capture(selection.kernel.fn, K.FamilyTiling()))
+    assert plan == GemmPlan("a", "b", "c", krn.f16, krn.f32, (128, 128, 64), False)
+    with krn.configure(**{"run.variants": {"gemm": "portable"}}):
+        assert K.gemm.select(b200).name == "portable" and K.gemm.select(b200).reason == "pinned by run.variants"
+    with krn.configure(**{"run.variants": {"gemm": "gemm_hopper"}}):
+        assert K.gemm.select(b200).kernel is K.gemm_hopper
+    with krn.configure(**{"run.variants": {"gemm": "nonesuch"}}), pytest.raises(LookupError, match="nonesuch"):
+        K.gemm.select(b200)
+
+    @K.gemm.variant(targets.Nvidia, requires={F.BLOCK_SCALED_MMA})
+    def gemm_rival(t: K.FamilyTiling, a, b, c) -> None: ...
+
+    try:
+        with pytest.raises(AmbiguousVariant, match="gemm on sm_100a: gemm_rival, gemm_tensor_memory tie"):
+            K.gemm.select(b200)
+        assert K.gemm.select(hopper).name == "gemm_hopper"  # the tie only exists where both rules match
+    finally:
+        del K.gemm.variants["gemm_rival"]
+
+
 def test_library_candidate_protocol() -> None:
     """Names, refusals and flags of the one matmul candidate (protocol of src/krn/lib/lib.py:201-235)."""
     from krn_b200 import lib
