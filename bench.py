@@ -240,9 +240,13 @@ class GemmFp8(Workload):
         self.b, self.sb = self._quantize(b, 128)
         del b
         self.c_local = torch.empty((self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+        self.fused = None
         if world > 1:
-            self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
-            self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+            if os.environ.get("KRN_B200_GATHER", "fused") == "fused":
+                self.fused = sharding.GatheredProduct(self.m, self.n, torch.bfloat16, multiple=256)
+            else:
+                self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
+                self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
             self.launches_per_step = 2
 
     def _quantize(self, x, block_rows: int):
@@ -258,8 +262,10 @@ class GemmFp8(Workload):
     @property
     def config(self) -> dict:
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
-                "sharding": f"N-column blocks x{self.world}, NCCL all-gather of the output columns" if self.world > 1
-                else "one GPU, no exchange",
+                "sharding": (f"N-column blocks x{self.world}, " + (
+                    "all-gather of the output columns fused into the product kernel (TMA stores into every rank's C over "
+                    "NVLink) + device barrier" if self.fused else "NCCL all-gather of the output columns + re-layout kernel"))
+                if self.world > 1 else "one GPU, no exchange",
                 "l2": self.l2_note("operands and output", self.m * self.k + self.n_local * self.k + 2 * self.m * (
                     self.n if self.world > 1 else self.n_local), 1)}
 
@@ -274,6 +280,9 @@ class GemmFp8(Workload):
 
     def step(self, calls) -> None:
         stream = self.torch.cuda.current_stream()
+        if self.fused is not None:
+            self.fused.run_fp8(self.a, self.sa, self.b, self.sb, stream)
+            return
         calls.gemm_fp8_blockscaled_tn(self.a, self.sa, self.b, self.sb, self.c_local, stream)
         if self.world > 1:
             from krn_b200 import sharding

@@ -121,6 +121,17 @@ int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa,
                                      void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
                                      int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream);
 
+/* The block-scaled FP8 product sharded by output columns with the all-gather of the columns done by the kernel's
+ * epilogue, exactly as krn_b200_gemm_tn_gather does for the 16-bit product: rank `rank` multiplies A by ITS rows of B
+ * (b: [n_local, K] codes, sb: [n_local / 128, ceil(K/128)] scales) and stores the column block
+ * [rank * n_local, (rank + 1) * n_local) into every rank's C (c_of_rank: a HOST array of `ranks` addresses valid on
+ * this device; TMA stores over NVLink, no peer loads, nothing multicast). n_local must be a multiple of 128. A
+ * cross-rank barrier after the call makes every C complete. No counterpart in the reference. */
+int krn_b200_gemm_fp8_blockscaled_tn_gather(int c_type, const void* a, const float* sa, const void* b, const float* sb,
+                                            void* const* c_of_rank, int ranks, int rank, int64_t m, int64_t n_local,
+                                            int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                                            void* stream);
+
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (batch, q head), the statement
  * sequence of the reference's example kernel (examples/04_libraries/08_flash_attention.py:44-59): scores
  * carry scale_log2 = log2(e)/sqrt(d) so every exponential is exp2, masked scores take -1.0e30, running

@@ -13,6 +13,18 @@ struct Problem {
   int b_kn;  // 0: b is (N, K), the operand of `b.transpose()`; 1: b is (K, N), the operand of a plain `a @ b`
 };
 
+// Where the output goes. One map for a plain product. When the product is sharded by output columns over the GPUs
+// of a node, one map per rank: every rank's full C (its own and, through NVLink peer mappings, the others'),
+// and this rank's column block is stored into all of them at `column_offset` — the all-gather of the output
+// columns happens in the epilogue's TMA stores, tile by tile, while the main loop works on the next tile.
+// (TMA STORES to peer memory; no load ever targets a peer and nothing is multicast.)
+constexpr int kMaxDestinations = 8;
+struct Destinations {
+  CUtensorMap maps[kMaxDestinations];
+  int count;
+  int column_offset;
+};
+
 // What happens to the f32 accumulator between the last K step and the rounding to the output type:
 // `out = activation(acc + bias[column])`, the statements of the reference's `matmul_epilogue` kernel
 // (src/krn/lib/lib_kernels.py:30-48). flags = KRN_B200_EPILOGUE_* of include/krn_b200.h: bit 0 adds the bias (a

@@ -91,7 +91,7 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], int chunk, const ui
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_c, Problem p, Scales scales, DeviceStatus* status) {
+                const __grid_constant__ Destinations dst, Problem p, Scales scales, DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
 
@@ -134,7 +134,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
-    prefetch_tensormap(&map_c);
+    for (int d = 0; d < dst.count; ++d) prefetch_tensormap(&dst.maps[d]);
   }
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
@@ -402,7 +402,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (lane == 0) {
             const int col = col0 + chunk_index * kChunkCols;
             const int row = row0 + rows_half * 16;
-            if (row < p.m && col < p.n) tma_store_2d(&map_c, col, row, my_store);
+            if (row < p.m && col < p.n) {
+              // one box, every destination: the own output and, when sharded, each peer's copy of C
+              for (int d = 0; d < dst.count; ++d) tma_store_2d(&dst.maps[d], col + dst.column_offset, row, my_store);
+            }
             tma_store_commit();
           }
         }
@@ -428,7 +431,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
-int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
            Scales scales, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_fp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
@@ -481,10 +484,11 @@ int fp8_pair_mode(int64_t m) {
 }  // namespace
 }  // namespace krnb
 
-extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b,
-                                                const float* sb, void* c, int64_t m, int64_t n, int64_t k,
-                                                int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
-                                                void* stream_handle) {
+// Checks, tensor maps and launch shared by the plain and the column-sharded entry points: C_d[:, offset : offset + n]
+// for every destination d (each a row-major matrix of n_total columns with pitch ldc).
+static int fp8_product(int c_type, const void* a, const float* sa, const void* b, const float* sb,
+                       void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m, int64_t n,
+                       int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
@@ -492,26 +496,35 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
   }
   if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent");
   if (m == 0 || n == 0) return KRN_B200_OK;
-  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+  if (m > INT32_MAX || n_total > INT32_MAX || k > INT32_MAX) {
     return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
   }
-  if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr || sa == nullptr || sb == nullptr))) {
+  bool null_destination = false, aligned_destinations = true;
+  for (int d = 0; d < count; ++d) {
+    null_destination = null_destination || destinations[d] == nullptr;
+    aligned_destinations = aligned_destinations && aligned16(destinations[d]);
+  }
+  if (null_destination || (k > 0 && (a == nullptr || b == nullptr || sa == nullptr || sb == nullptr))) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
   const int64_t blocks_k = (k + 127) / 128;
-  if (ldc < n || (k > 0 && (lda < k || ldb < k || ldsa < blocks_k || ldsb < blocks_k))) {
+  if (ldc < n_total || (k > 0 && (lda < k || ldb < k || ldsa < blocks_k || ldsb < blocks_k))) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
   }
   DeviceContext* ctx = current_context();
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
   if (k == 0) {
-    zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(static_cast<uint8_t*>(c), n * c_bytes, ldc * c_bytes, m);
-    KRNB_CUDA(cudaGetLastError());
+    for (int d = 0; d < count; ++d) {
+      zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(
+          static_cast<uint8_t*>(destinations[d]) + column_offset * c_bytes, n * c_bytes, ldc * c_bytes, m);
+      KRNB_CUDA(cudaGetLastError());
+    }
     return KRN_B200_OK;
   }
-  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
+  if (!aligned16(a) || !aligned16(b) || !aligned_destinations || lda % 16 != 0 || ldb % 16 != 0 ||
+      (ldc * c_bytes) % 16 != 0) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT,
                 "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld bytes, ldc %lld elements)",
                 (long long)lda, (long long)ldb, (long long)ldc);
@@ -533,7 +546,7 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
   scales.ldsb = ldsb;
   scales.blocks_n = int((n + 127) / 128);
 
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b;
   {
     uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
     uint64_t strides[1] = {uint64_t(lda)};
@@ -546,21 +559,57 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
     uint32_t box[2] = {128, uint32_t(kBN / group)};
     if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  {
+  Destinations dst;
+  dst.count = count;
+  dst.column_offset = int(column_offset);
+  for (int d = 0; d < kMaxDestinations; ++d) {
     const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                      : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+    uint64_t dims[2] = {uint64_t(n_total), uint64_t(m)};
     uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
-    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+    // unused slots repeat the first destination so that every map in the struct is a valid descriptor
+    if (int rc = encode_tensor_map(&dst.maps[d], c_dt, 2, destinations[d < count ? d : 0], dims, strides, box,
+                                   Swizzle::k128B)) return rc;
   }
   if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, scales, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, stream);
   }
-  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
-  return launch<1, uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, stream);
+}
+
+extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b,
+                                                const float* sb, void* c, int64_t m, int64_t n, int64_t k,
+                                                int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                                                void* stream_handle) {
+  void* destinations[1] = {c};
+  return fp8_product(c_type, a, sa, b, sb, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, ldsa, ldsb, stream_handle);
+}
+
+extern "C" int krn_b200_gemm_fp8_blockscaled_tn_gather(int c_type, const void* a, const float* sa, const void* b,
+                                                       const float* sb, void* const* c_of_rank, int ranks, int rank,
+                                                       int64_t m, int64_t n_local, int64_t k, int64_t lda, int64_t ldb,
+                                                       int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle) {
+  using namespace krnb;
+  if (ranks < 1 || ranks > kMaxDestinations || rank < 0 || rank >= ranks || c_of_rank == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "rank %d of %d: between 1 and %d ranks are supported", rank, ranks,
+                kMaxDestinations);
+  }
+  if (m <= 0 || n_local <= 0 || k <= 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "extents must be positive (m %lld, n_local %lld, k %lld)", (long long)m,
+                (long long)n_local, (long long)k);
+  }
+  if (n_local % 128 != 0) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "a column block of %lld columns does not end on a 128-column scale block of b. "
+                "Instead: shard N in multiples of 128 columns", (long long)n_local);
+  }
+  void* destinations[kMaxDestinations];
+  for (int r = 0; r < ranks; ++r) destinations[r] = c_of_rank[r];
+  return fp8_product(c_type, a, sa, b, sb, destinations, ranks, rank * n_local, n_local * ranks, m, n_local, k, lda, ldb,
+                     ldc, ldsa, ldsb, stream_handle);
 }

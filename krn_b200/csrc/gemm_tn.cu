@@ -45,18 +45,6 @@ struct Layout {
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
 };
 
-// Where the output goes. One map for a plain product. When the product is sharded by output columns over the GPUs
-// of a node, one map per rank: every rank's full C (its own and, through NVLink peer mappings, the others'),
-// and this rank's column block is stored into all of them at `column_offset` — the all-gather of the output
-// columns happens in the epilogue's TMA stores, tile by tile, while the main loop works on the next tile.
-// (TMA STORES to peer memory; no load ever targets a peer and nothing is multicast.)
-constexpr int kMaxDestinations = 8;
-struct Destinations {
-  CUtensorMap maps[kMaxDestinations];
-  int count;
-  int column_offset;
-};
-
 enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
 
 // `values[i]` is this thread's accumulator for output column `col + i` (i < 32): add the bias of that column and apply

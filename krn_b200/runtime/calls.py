@@ -118,6 +118,23 @@ def gemm_fp8_blockscaled_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: An
     native.check(status, "block-scaled FP8 tile matrix product")
 
 
+def gemm_fp8_blockscaled_tn_gather(a: Any, sa: Any, b_local: Any, sb_local: Any, c_pointers: list[int], rank: int,
+                                   n_local: int, ldc: int, c_type: int, stream: Any = None) -> None:
+    """This rank's column block of the block-scaled FP8 product, stored by the kernel's epilogue into every rank's
+    full C (`c_pointers[r]` = address on this device of rank r's row-major C[m, len(c_pointers) * n_local])."""
+    (m, k), (nb, kb) = a.shape, b_local.shape
+    blocks = -(-k // 128)
+    if kb != k or nb != n_local or tuple(sa.shape) != (m, blocks) or tuple(sb_local.shape) != (-(-n_local // 128), blocks):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b_local.shape)}, scales "
+                         f"{tuple(sa.shape)}, {tuple(sb_local.shape)}")
+    ranks = len(c_pointers)
+    array = (ctypes.c_void_p * ranks)(*c_pointers)
+    status = native.library().krn_b200_gemm_fp8_blockscaled_tn_gather(
+        c_type, _pointer(a), _pointer(sa), _pointer(b_local), _pointer(sb_local), array, ranks, rank, m, n_local, k,
+        _pitch(a), _pitch(b_local), ldc, _pitch(sa), _pitch(sb_local), _stream(stream))
+    native.check(status, "column-sharded block-scaled FP8 tile matrix product")
+
+
 def _strides3(tensor: Any) -> Any:
     strides = tuple(tensor.stride()) if callable(getattr(tensor, "stride", None)) else tuple(tensor.strides)
     if len(strides) != 4 or strides[3] != 1:

@@ -64,7 +64,7 @@ class GatheredProduct:
     all ranks' C from its epilogue, tile by tile, and a device-side barrier across the ranks follows on the same
     stream. After `run` returns (stream-ordered) `self.c` holds the whole product on every rank."""
 
-    def __init__(self, m: int, n: int, dtype: Any, group: Any = None) -> None:
+    def __init__(self, m: int, n: int, dtype: Any, group: Any = None, multiple: int = 64) -> None:
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
@@ -72,7 +72,7 @@ class GatheredProduct:
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.m, self.n = m, n
-        begin, end = column_block(n, self.rank, self.world, 64)
+        begin, end = column_block(n, self.rank, self.world, multiple)
         self.n_local = end - begin
         self.c = symm.empty((m, n), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
         self.handle = symm.rendezvous(self.c, self.group)
@@ -85,5 +85,15 @@ class GatheredProduct:
         from krn_b200.runtime import calls
 
         calls.gemm_tn_gather(a, b_local, self.pointers, self.rank, self.m, self.n_local, self.n, self.c_type, stream)
+        self.handle.barrier()
+        return self.c
+
+    def run_fp8(self, a: Any, sa: Any, b_local: Any, sb_local: Any, stream: Any = None) -> Any:
+        """The block-scaled FP8 product through the same destinations (construct with `multiple=128`: a column block
+        must end on a scale block of b)."""
+        from krn_b200.runtime import calls
+
+        calls.gemm_fp8_blockscaled_tn_gather(a, sa, b_local, sb_local, self.pointers, self.rank, self.n_local, self.n,
+                                             self.c_type, stream)
         self.handle.barrier()
         return self.c

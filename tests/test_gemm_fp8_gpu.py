@@ -89,3 +89,32 @@ def test_k_zero_and_ragged_edges_leave_neighbours_alone(cuda) -> None:
     assert bool((c[33:] == 5).all()) and bool((c[:, 24:] == 5).all())
     want = o.bf16_values(o.gemm_fp8_blockscaled(a_codes, sa, b_codes, sb))
     assert o.rel_frobenius(c[:33, :24].float().cpu().numpy(), want) < 1e-2
+
+
+def test_column_sharded_fp8_product_stores_into_every_destination(cuda) -> None:
+    """The sharded entry point on one GPU: two "ranks" are two launches, each storing its column block into both
+    destination buffers; both copies must equal the unsharded product bit for bit."""
+    torch = cuda
+    from krn_b200.runtime import native
+
+    m, n, k, ranks = 384, 1024, 512, 2
+    a_codes, sa, b_codes, sb = o.config_gemm_fp8(m, n, k, seed=41)
+    fp8 = torch.float8_e4m3fn
+    a, b = torch.from_numpy(a_codes).cuda().view(fp8), torch.from_numpy(b_codes).cuda().view(fp8)
+    dsa, dsb = torch.from_numpy(sa).cuda(), torch.from_numpy(sb).cuda()
+    whole = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    calls.gemm_fp8_blockscaled_tn(a, dsa, b, dsb, whole)
+    copies = [torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(ranks)]
+    pointers = [int(c.data_ptr()) for c in copies]
+    width = n // ranks
+    for rank in range(ranks):
+        rows = slice(rank * width, (rank + 1) * width)
+        calls.gemm_fp8_blockscaled_tn_gather(a, dsa, b[rows], dsb[rank * width // 128:(rank + 1) * width // 128], pointers,
+                                             rank, width, n, native.BF16)
+        torch.cuda.synchronize()
+        if rank == 0:
+            assert all(bool(torch.isnan(c[:, width:].float()).all()) for c in copies)  # the other block is untouched
+    for c in copies:
+        assert torch.equal(c, whole)
+    with pytest.raises(Exception, match="scale block"):
+        calls.gemm_fp8_blockscaled_tn_gather(a, dsa, b[:192], dsb[:2], pointers, 0, 192, n, native.BF16)
