@@ -23,6 +23,8 @@ struct Destinations {
   CUtensorMap maps[kMaxDestinations];
   int count;
   int column_offset;
+  int first;  // destination the stores of a box start with: each rank starts one past itself, so that at any moment
+              // the ranks of a node aim at different receivers instead of all at rank 0, then all at rank 1, ...
 };
 
 // What happens to the f32 accumulator between the last K step and the rounding to the output type:

@@ -404,7 +404,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int row = row0 + rows_half * 16;
             if (row < p.m && col < p.n) {
               // one box, every destination: the own output and, when sharded, each peer's copy of C
-              for (int d = 0; d < dst.count; ++d) tma_store_2d(&dst.maps[d], col + dst.column_offset, row, my_store);
+              int d = dst.first;
+              for (int i = 0; i < dst.count; ++i) {
+                tma_store_2d(&dst.maps[d], col + dst.column_offset, row, my_store);
+                if (++d == dst.count) d = 0;
+              }
             }
             tma_store_commit();
           }
@@ -562,6 +566,7 @@ static int fp8_product(int c_type, const void* a, const float* sa, const void* b
   Destinations dst;
   dst.count = count;
   dst.column_offset = int(column_offset);
+  dst.first = count > 1 ? int((column_offset / n + 1) % count) : 0;  // column_offset / n = this rank
   for (int d = 0; d < kMaxDestinations; ++d) {
     const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                      : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16

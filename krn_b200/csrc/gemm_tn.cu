@@ -297,7 +297,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) {
             // one box, every destination: the own output and, when sharded, each peer's copy of C
-            for (int d = 0; d < dst.count; ++d) tma_store_2d(&dst.maps[d], col + dst.column_offset, row0, buffer);
+            int d = dst.first;
+            for (int i = 0; i < dst.count; ++i) {
+              tma_store_2d(&dst.maps[d], col + dst.column_offset, row0, buffer);
+              if (++d == dst.count) d = 0;
+            }
             tma_store_commit();
           }
           ++stores;
@@ -481,6 +485,7 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
   Destinations dst;
   dst.count = count;
   dst.column_offset = int(column_offset);
+  dst.first = count > 1 ? int((column_offset / n + 1) % count) : 0;  // column_offset / n = this rank
   for (int d = 0; d < kMaxDestinations; ++d) {
     const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                      : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
