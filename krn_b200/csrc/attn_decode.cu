@@ -340,6 +340,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       out[2 + tid] = acc[h];
     }
   }
+  // the merge kernel is launched as a programmatic dependent: let it start arriving while the last CTAs drain
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (*abort_flag != 0) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -359,6 +361,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ workspace, const i
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int len = context_len[b];
   const int used = min(chunks, (len + kChunkTokens - 1) / kChunkTokens);
+  // launched with programmatic stream serialisation: this grid may be resident before the partial kernel has
+  // finished; the partials are valid only after this wait (inputs of the call itself are read above it)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const float* unit = workspace + ((long long)b * q_heads + h) * chunks * (kD + 2);
   float m = -INFINITY;
   for (int c = 0; c < used; ++c) m = fmaxf(m, unit[c * (kD + 2)]);
@@ -371,6 +376,23 @@ __global__ void decode_merge_kernel(const float* __restrict__ workspace, const i
   const float vs = v_scale[b * kv_heads + h / (q_heads / kv_heads)];
   const float value = used > 0 ? num / den * vs : 0.f;
   o[((long long)b * q_heads + h) * kD + d] = uint16_t(pack_bf16x2(value, 0.f) & 0xffffu);
+}
+
+// The merge launch overlaps its own launch latency with the tail of the partial kernel (programmatic dependent launch).
+int launch_merge(const float* workspace, const int32_t* context_len, const float* v_scale, uint16_t* o, int q_heads,
+                 int kv_heads, int batch, int chunks, cudaStream_t stream) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(q_heads), unsigned(batch), 1);
+  config.blockDim = dim3(kD, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  KRNB_CUDA(cudaLaunchKernelEx(&config, decode_merge_kernel, workspace, context_len, v_scale, o, q_heads, kv_heads, chunks));
+  return KRN_B200_OK;
 }
 
 int encode_pages(CUtensorMap* map, const void* pages, int64_t num_pages, int64_t kv_heads) {
@@ -451,10 +473,8 @@ extern "C" int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages
   decode_partial_kernel<<<dim3(unsigned(p.chunks), unsigned(kv_heads), unsigned(batch)), kThreads, kSmemBytes, stream>>>(
       map_k, map_v, p, ctx->status_dev);
   KRNB_CUDA(cudaGetLastError());
-  decode_merge_kernel<<<dim3(unsigned(q_heads), unsigned(batch)), kD, 0, stream>>>(
-      p.workspace, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads), p.chunks);
-  KRNB_CUDA(cudaGetLastError());
-  return KRN_B200_OK;
+  return launch_merge(p.workspace, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads),
+                      int(batch), p.chunks, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -573,8 +593,6 @@ extern "C" int krn_b200_attn_decode_fp8_paged_noalloc(const void* q, const void*
   decode_partial_kernel<<<dim3(unsigned(p.chunks), unsigned(kv_heads), unsigned(batch)), kThreads, kSmemBytes, stream>>>(
       map_k, map_v, p, status);
   KRNB_CUDA(cudaGetLastError());
-  decode_merge_kernel<<<dim3(unsigned(q_heads), unsigned(batch)), kD, 0, stream>>>(
-      scratch, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads), p.chunks);
-  KRNB_CUDA(cudaGetLastError());
-  return KRN_B200_OK;
+  return launch_merge(scratch, context_len, v_scale, static_cast<uint16_t*>(o), int(q_heads), int(kv_heads), int(batch),
+                      p.chunks, stream);
 }
