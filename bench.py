@@ -521,7 +521,8 @@ def reference_arm(args, rank: int) -> int:
         "impl": "reference", "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic",
-        "config": {"workload": workload.description},
+        "config": {"workload": workload.description,
+                   **{key: getattr(kind, key) for key in ("m", "n", "k") if hasattr(kind, key)}},
         "cpu_baseline": {"value": value, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
