@@ -199,8 +199,14 @@ class GemmBf16(Workload):
 
         self.host_in = [t.cpu().pin_memory() for t in (self.a, self.b)]
         self.host_out = self.torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
-        self.streamed = streaming.StreamedProduct(self.m, self.n_local, self.k, self.torch.bfloat16)
-        return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
+        if self.world > 1 and self.m % self.world == 0:
+            # a crosses PCIe once per node: each rank copies M / G of its rows, NVLink all-gathers them
+            self.streamed = streaming.ShardedStreamedProduct(self.m, self.n_local, self.k, self.torch.bfloat16)
+            h2d = (self.host_in[0].numel() // self.world + self.host_in[1].numel()) * 2
+        else:
+            self.streamed = streaming.StreamedProduct(self.m, self.n_local, self.k, self.torch.bfloat16)
+            h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        return h2d, self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
         self.streamed.run(self.host_in[0], self.host_in[1], self.host_out)

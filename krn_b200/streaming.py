@@ -109,6 +109,58 @@ class StreamedProduct:
         current.wait_stream(s.d2h)
 
 
+class ShardedStreamedProduct:
+    """The column-sharded product of a node with host operands: rank r of G returns `c_host[:, block r] = a_host @
+    b_host[block r]^T` (its rows of `b`, its column block of `c`).
+
+    Every rank needs all of `a`, but `a` should cross PCIe once per node, not once per GPU (eight GPUs pulling the
+    same 128 MiB through the host at once were slower end to end than one GPU alone). So rank r copies only rows
+    [r M/G, (r+1) M/G) of `a_host`, the row blocks are all-gathered between the GPUs over NVLink (NCCL, in place in
+    the device copy of `a`), and the rank's rows of `b` stream in panels behind it with the products and the
+    device→host copies of the finished column slabs overlapped as in `StreamedProduct`. M must divide by G."""
+
+    def __init__(self, m: int, n_local: int, k: int, dtype: Any, out_dtype: Any = None, panels: int = 8,
+                 group: Any = None) -> None:
+        torch = _torch()
+        import torch.distributed as dist
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if m % self.world:
+            raise ValueError(f"{m} rows of a do not divide over {self.world} ranks")
+        self.m, self.n, self.k = m, n_local, k
+        self.rows = (self.rank * (m // self.world), (self.rank + 1) * (m // self.world))
+        self.a = torch.empty((m, k), device="cuda", dtype=dtype)
+        self.b = torch.empty((n_local, k), device="cuda", dtype=dtype)
+        self.c = torch.empty((m, n_local), device="cuda", dtype=out_dtype or dtype)
+        self.ranges = _panels(n_local, panels, 256)
+        self.streams = _Streams()
+
+    def run(self, a_host: Any, b_host: Any, c_host: Any) -> None:
+        torch = _torch()
+        import torch.distributed as dist
+
+        current = torch.cuda.current_stream()
+        s = self.streams
+        lo_a, hi_a = self.rows
+        s.h2d.wait_stream(current)
+        with torch.cuda.stream(s.h2d):
+            self.a[lo_a:hi_a].copy_(a_host[lo_a:hi_a], non_blocking=True)
+            s.event(0).record(s.h2d)
+            for index, (lo, hi) in enumerate(self.ranges):
+                self.b[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
+                s.event(2 * index + 2).record(s.h2d)
+        current.wait_event(s.event(0))
+        dist.all_gather_into_tensor(self.a, self.a[lo_a:hi_a], group=self.group)  # in place: the slice is the input
+        for index, (lo, hi) in enumerate(self.ranges):
+            current.wait_event(s.event(2 * index + 2))
+            calls.gemm_tn(self.a, self.b[lo:hi], self.c[:, lo:hi], current)
+            s.event(2 * index + 3).record(current)
+            s.d2h.wait_event(s.event(2 * index + 3))
+            _copy_out(c_host[:, lo:hi], self.c[:, lo:hi], s.d2h)
+        current.wait_stream(s.d2h)
+
+
 class StreamedFp8Product:
     """The block-scaled FP8 product with host operands: codes and scales of `a` (1x128 blocks) go first, then row
     panels of `b` (codes + their 128x128 block scales, panel boundaries on multiples of 256 rows); column slabs of

@@ -1,0 +1,84 @@
+"""Two ranks on two GPUs: the column-sharded product with the all-gather fused into the kernel's epilogue, and the
+sharded host-operand path whose `a` is all-gathered over NVLink. Skipped on a machine with one GPU (the sharded entry
+points themselves are also exercised on one GPU in tests/test_gemm_gpu.py and tests/test_gemm_fp8_gpu.py)."""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank(rank: int, world: int, port: int, failures) -> None:
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from krn_b200 import sharding, streaming
+        from krn_b200.runtime import calls
+
+        m, n, k = 512, 1024, 328
+        gen = torch.Generator().manual_seed(5)
+        a_host = torch.randint(-4, 5, (m, k), generator=gen).to(torch.bfloat16).pin_memory()
+        b_host = torch.randint(-4, 5, (n, k), generator=gen).to(torch.bfloat16).pin_memory()
+        a, b = a_host.cuda(), b_host.cuda()
+        whole = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+        calls.gemm_tn(a, b, whole)
+        begin, end = sharding.column_block(n, rank, world, 64)
+
+        fused = sharding.GatheredProduct(m, n, torch.bfloat16)
+        fused.c.fill_(float("nan"))
+        dist.barrier()
+        result = fused.run(a, b[begin:end])
+        torch.cuda.synchronize()
+        if not torch.equal(result, whole):
+            failures.put(f"rank {rank}: the fused gather does not hold the whole product")
+
+        streamed = streaming.ShardedStreamedProduct(m, end - begin, k, torch.bfloat16, panels=2)
+        c_host = torch.full((m, end - begin), float("nan"), dtype=torch.bfloat16).pin_memory()
+        zeros = torch.zeros_like(a_host)
+        zeros[streamed.rows[0]:streamed.rows[1]] = a_host[streamed.rows[0]:streamed.rows[1]]
+        streamed.run(zeros, b_host[begin:end], c_host)  # only this rank's rows of a are read from ITS host copy
+        torch.cuda.synchronize()
+        if not torch.equal(c_host, whole[:, begin:end].cpu()):
+            failures.put(f"rank {rank}: the sharded host-operand product differs from the one-GPU product")
+    except Exception as error:  # reported to the parent, which fails the test
+        failures.put(f"rank {rank}: {type(error).__name__}: {error}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_fused_gather_and_sharded_streaming(cuda) -> None:
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    context = mp.get_context("spawn")
+    failures = context.Queue()
+    port = _free_port()
+    workers = [context.Process(target=_rank, args=(rank, 2, port, failures)) for rank in range(2)]
+    for w in workers:
+        w.start()
+    for w in workers:
+        w.join(timeout=180)
+    hung = [w for w in workers if w.is_alive()]
+    for w in hung:
+        w.terminate()  # our own children, by handle
+    problems = []
+    while not failures.empty():
+        problems.append(failures.get())
+    assert not hung and not problems and all(w.exitcode == 0 for w in workers), problems
