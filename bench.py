@@ -306,8 +306,14 @@ class GemmFp8(Workload):
         self.host_in = [t.view(torch.uint8).cpu().pin_memory() if t.dtype == torch.float8_e4m3fn else t.cpu().pin_memory()
                         for t in (self.a, self.sa, self.b, self.sb)]
         self.host_out = torch.empty(self.c_local.shape, dtype=self.c_local.dtype).pin_memory()
-        self.streamed = streaming.StreamedFp8Product(self.m, self.n_local, self.k, self.c_local.dtype)
-        return sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size()
+        h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        if self.world > 1 and self.m % self.world == 0:
+            # a and its scales cross PCIe once per node: each rank copies M / G of the rows, NVLink all-gathers them
+            self.streamed = streaming.ShardedStreamedFp8Product(self.m, self.n_local, self.k, self.c_local.dtype)
+            h2d -= sum(t.numel() * t.element_size() for t in self.host_in[:2]) * (self.world - 1) // self.world
+        else:
+            self.streamed = streaming.StreamedFp8Product(self.m, self.n_local, self.k, self.c_local.dtype)
+        return h2d, self.host_out.numel() * self.host_out.element_size()
 
     def e2e_step(self, calls) -> None:
         self.streamed.run(*self.host_in, self.host_out)

@@ -202,6 +202,60 @@ class StreamedFp8Product:
         current.wait_stream(s.d2h)
 
 
+class ShardedStreamedFp8Product:
+    """The column-sharded block-scaled FP8 product with host operands, as `ShardedStreamedProduct`: rank r copies only
+    its M/G rows of `a` (codes and 1x128 scales), NCCL all-gathers both over NVLink, and the rank's rows of `b` (codes
+    and 128x128 scales) stream in panels with the column slabs of its block of `c` returning as they finish."""
+
+    def __init__(self, m: int, n_local: int, k: int, out_dtype: Any, panels: int = 8, group: Any = None) -> None:
+        torch = _torch()
+        import torch.distributed as dist
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if m % self.world:
+            raise ValueError(f"{m} rows of a do not divide over {self.world} ranks")
+        self.m, self.n, self.k = m, n_local, k
+        self.rows = (self.rank * (m // self.world), (self.rank + 1) * (m // self.world))
+        blocks_k = -(-k // 128)
+        self.a = torch.empty((m, k), device="cuda", dtype=torch.uint8)
+        self.sa = torch.empty((m, blocks_k), device="cuda", dtype=torch.float32)
+        self.b = torch.empty((n_local, k), device="cuda", dtype=torch.uint8)
+        self.sb = torch.empty((-(-n_local // 128), blocks_k), device="cuda", dtype=torch.float32)
+        self.c = torch.empty((m, n_local), device="cuda", dtype=out_dtype)
+        self.ranges = _panels(n_local, panels, 256)
+        self.streams = _Streams()
+
+    def run(self, a_host: Any, sa_host: Any, b_host: Any, sb_host: Any, c_host: Any) -> None:
+        torch = _torch()
+        import torch.distributed as dist
+
+        current = torch.cuda.current_stream()
+        s = self.streams
+        lo_a, hi_a = self.rows
+        s.h2d.wait_stream(current)
+        with torch.cuda.stream(s.h2d):
+            self.a[lo_a:hi_a].copy_(a_host[lo_a:hi_a], non_blocking=True)
+            self.sa[lo_a:hi_a].copy_(sa_host[lo_a:hi_a], non_blocking=True)
+            s.event(0).record(s.h2d)
+            for index, (lo, hi) in enumerate(self.ranges):
+                self.b[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
+                self.sb[lo // 128:-(-hi // 128)].copy_(sb_host[lo // 128:-(-hi // 128)], non_blocking=True)
+                s.event(2 * index + 2).record(s.h2d)
+        current.wait_event(s.event(0))
+        dist.all_gather_into_tensor(self.a, self.a[lo_a:hi_a], group=self.group)
+        dist.all_gather_into_tensor(self.sa, self.sa[lo_a:hi_a], group=self.group)
+        fp8 = torch.float8_e4m3fn
+        for index, (lo, hi) in enumerate(self.ranges):
+            current.wait_event(s.event(2 * index + 2))
+            calls.gemm_fp8_blockscaled_tn(self.a.view(fp8), self.sa, self.b[lo:hi].view(fp8),
+                                          self.sb[lo // 128:-(-hi // 128)], self.c[:, lo:hi], current)
+            s.event(2 * index + 3).record(current)
+            s.d2h.wait_event(s.event(2 * index + 3))
+            _copy_out(c_host[:, lo:hi], self.c[:, lo:hi], s.d2h)
+        current.wait_stream(s.d2h)
+
+
 class StreamedAttention:
     """Flash-attention forward over host tensors q, o (batch, q_heads, seq, d) and k, v (batch, kv_heads, seq, d),
     streamed one group of batches at a time (batches are independent, so nothing is copied whole)."""

@@ -55,6 +55,23 @@ def _rank(rank: int, world: int, port: int, failures) -> None:
         torch.cuda.synchronize()
         if not torch.equal(c_host, whole[:, begin:end].cpu()):
             failures.put(f"rank {rank}: the sharded host-operand product differs from the one-GPU product")
+
+        import numpy as np
+        from oracle import oracle as o
+
+        a_codes, sa, b_codes, sb = o.config_gemm_fp8(256, 1024, 512, seed=6)
+        hosts = [torch.from_numpy(x).pin_memory() for x in (a_codes, sa, b_codes, sb)]
+        fp8 = torch.float8_e4m3fn
+        whole8 = torch.empty((256, 1024), device="cuda", dtype=torch.bfloat16)
+        calls.gemm_fp8_blockscaled_tn(hosts[0].cuda().view(fp8), hosts[1].cuda(), hosts[2].cuda().view(fp8), hosts[3].cuda(),
+                                      whole8)
+        begin8, end8 = sharding.column_block(1024, rank, world, 256)
+        product8 = streaming.ShardedStreamedFp8Product(256, end8 - begin8, 512, torch.bfloat16, panels=2)
+        c8 = torch.full((256, end8 - begin8), float("nan"), dtype=torch.bfloat16).pin_memory()
+        product8.run(hosts[0], hosts[1], hosts[2][begin8:end8], hosts[3][begin8 // 128:end8 // 128], c8)
+        torch.cuda.synchronize()
+        if not torch.equal(c8, whole8[:, begin8:end8].cpu()):
+            failures.put(f"rank {rank}: the sharded host-operand FP8 product differs from the one-GPU product")
     except Exception as error:  # reported to the parent, which fails the test
         failures.put(f"rank {rank}: {type(error).__name__}: {error}")
     finally:
