@@ -10,15 +10,19 @@ Hkv=8, S=4096, D=128), `attn_decode` (paged FP8 decode, 64 sequences, contexts 1
 
 Keys of the line:
   value         whole-job throughput with operands resident in HBM (CUDA events on the launching stream, max over ranks)
-  e2e           the same metric through the C-ABI call with HOST buffers: every step copies the operands from pinned
-                host memory, runs the kernel and reads the result back, all inside the timed region
+  e2e           the same metric through the public host-operand API (krn_b200.streaming) with HOST buffers: every step
+                copies the operands from pinned host memory, runs the kernels and reads the result back, all inside the
+                timed region (panels of the copies overlap the kernels)
   roofline      achieved vs measured peak for the dominant kernel (algorithmic FLOPs or bytes / event time)
   cpu_baseline  the CPU restatement of the reference's C backend timed on this machine's cores on a bounded sample
   clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) total work is fixed ("strong" scaling): the tile
-products are sharded by output column blocks, all-gathered over NCCL and laid out as one row-major C on every rank;
-attention is sharded by (batch, kv head) and decode by sequence, with no collective.
+products are sharded by output column blocks and every rank ends with the whole row-major C — the all-gather of the
+column blocks is done by the product kernel's own epilogue (TMA stores into every rank's C over NVLink, then a device
+barrier; KRN_B200_GATHER=nccl selects an NCCL all-gather + re-layout kernel instead); attention is sharded by (batch,
+kv head) and decode by sequence, with no collective. The end-to-end leg of the products copies `a` once per node (each
+rank its share of the rows, all-gathered over NVLink).
 
 `--impl reference` times the reference's CPU implementation of the path (its C backend restated in oracle/, since
 the reference itself needs Python 3.14 + clang and holds no C sources) on the host cores, rank 0 only.
