@@ -195,3 +195,15 @@ def test_settings_and_no_cpu_fallback(monkeypatch) -> None:
     if not torch.cuda.is_available():
         with pytest.raises(TargetError, match="no CPU fallback"):
             krn.host.Device.current()
+
+
+def test_streaming_panels_cover_the_extent_on_tile_boundaries() -> None:
+    """Panel ranges of the host-operand streaming: contiguous, covering, boundaries on the requested multiple."""
+    from krn_b200.streaming import _panels
+
+    for extent, count, multiple in ((8192, 16, 256), (3584, 8, 256), (1024, 8, 256), (1100, 3, 256), (300, 16, 256), (8, 8, 1),
+                                    (28672, 16, 256)):
+        ranges = _panels(extent, count, multiple)
+        assert ranges[0][0] == 0 and ranges[-1][1] == extent and len(ranges) <= count
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:])) and all(hi > lo for lo, hi in ranges)
+        assert all(lo % multiple == 0 for lo, _ in ranges)
