@@ -1,5 +1,5 @@
-"""Explicit launch overrides: how many threads and blocks a kernel runs with `launch=`
-(src/krn/frontend/geometry.py:8-41)."""
+"""The three ways a call can state its launch size with `launch=` instead of having it inferred from the kernel
+body. Field names and the `Tiles.blocks` axis order are those of src/krn/frontend/geometry.py:8-41."""
 
 from __future__ import annotations
 
@@ -12,14 +12,14 @@ def ceildiv(a: int, b: int) -> int:
 
 @dataclass(frozen=True)
 class Items:
-    """Launch one thread per item and let the device profile choose block and grid size."""
+    """`count` independent work items, one thread each; how they are grouped into blocks is the device's choice."""
 
     count: int
 
 
 @dataclass(frozen=True)
 class Blocks:
-    """Launch an explicit grid of blocks."""
+    """A grid given outright: `x`, `y`, `z` blocks, optionally with the number of threads per block."""
 
     x: int
     y: int = 1
@@ -29,9 +29,11 @@ class Blocks:
 
 @dataclass(frozen=True)
 class Tiles:
-    """Launch one block per tile of an output: `Tiles(c.shape, (bm, bn))` covers a matrix with ceiling division.
+    """A grid derived from an output: enough `tile`-sized blocks to cover `shape`, rounding up on every axis, e.g.
+    `Tiles(c.shape, (bm, bn))`.
 
-    The last axis runs along x, the one before it along y, so a block's `block.tile(bm, bn)` is the tile it owns."""
+    Grid axes are assigned from the back — columns become x, rows y — which is the order `block.tile(bm, bn)` uses
+    inside the kernel, so each block lands on the tile it computes."""
 
     shape: tuple[int, ...]
     tile: tuple[int, ...]

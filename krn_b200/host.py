@@ -1,5 +1,4 @@
-"""`krn.host`: where kernels run (src/krn/runtime/host.py). `host.Device.current()` is the B200 device."""
+"""`krn.host`: short spelling of `krn.runtime.host` (`from krn import host`, src/krn/__init__.py)."""
 
-from krn_b200.runtime.api import Bound, Device, Event, Graph, Launcher, Stream
-
-__all__ = ["Bound", "Device", "Event", "Graph", "Launcher", "Stream"]
+from krn_b200.runtime.host import *  # noqa: F401,F403
+from krn_b200.runtime.host import __all__  # noqa: F401
