@@ -35,6 +35,7 @@ extern "C" {
 #define KRN_B200_F16 1
 #define KRN_B200_BF16 2
 #define KRN_B200_E4M3 3
+#define KRN_B200_E5M2 4
 
 /* Replaces the reference's version probes of its compiled artefacts (digest of nvrtc version + flags,
  * src/krn/runtime/cuda_backend.py:695-747): the host checks the ABI number before binding prototypes. */
@@ -75,6 +76,21 @@ int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void
  * K == 0. */
 int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
                      int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* C = A * B for two 8-bit float tiles loaded as they are stored — no scales, every code stands for its own value:
+ * the product the reference captures for fp8 pairs that are direct tile loads
+ * (`acc += a8[rows, ks] @ b8[ks, cols]`, src/krn/compiler/capture.py:3185-3192) and lowers to one unscaled
+ * m16n8k32 e4m3/e5m2 instruction per fragment (src/krn/compiler/cuda.py:207-227); here tcgen05 kind::f8f6f4
+ * accumulates the whole K extent in tensor memory.
+ *   a_type, b_type  KRN_B200_E4M3 or KRN_B200_E5M2, chosen per operand (all four pairs, as the reference tests,
+ *                   tests/compiler/test_tensor_cores.py:146,219-239)
+ *   b_kn            0: b is (N, K), the operand of b.transpose(); 1: b is (K, N) row-major, the form the reference's
+ *                   fp8 kernels write
+ *   lda/ldb/ldc     row pitches in ELEMENTS; 16-byte aligned addresses and pitches take the tensor-core kernel,
+ *                   anything else (the reference's 50 x 38 x 70 card) the plain fma kernel, which follows the
+ *                   reference's k-ordered chain exactly. K == 0 stores zeros. Ragged edges as krn_b200_gemm_tn. */
+int krn_b200_gemm_fp8(int a_type, int b_type, int c_type, int b_kn, const void* a, const void* b, void* c, int64_t m,
+                      int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
 /* epilogue flags of krn_b200_matmul: KRN_B200_EPILOGUE_BIAS may be or-ed with one activation */
 #define KRN_B200_EPILOGUE_NONE 0

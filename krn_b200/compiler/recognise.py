@@ -35,6 +35,7 @@ class GemmPlan:
     transposed_b: bool = True
     bias: str | None = None        # vector added to every row of the accumulator before the store
     activation: str | None = None  # "relu", "gelu" or "silu", applied after the bias
+    operand_b: Dtype | None = None  # b's element type for an fp8 pair (which may mix e4m3 and e5m2), else None
 
 
 @dataclass(frozen=True)
@@ -135,13 +136,18 @@ def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
     if value != init.var or len(store.index) != 2 or _block_tile(store.index[0], "y") != bm \
             or _block_tile(store.index[1], "x") != bn:
         return None
-    if a.dtype != b.dtype:
+    fp8 = ("f8e4m3fn", "f8e5m2")
+    if a.dtype.name in fp8 and b.dtype.name in fp8:
+        # fp8 pairs loaded directly multiply as stored, each operand in its own format
+        # (src/krn/compiler/capture.py:3185-3192, src/krn/compiler/cuda.py:207-227)
+        pass
+    elif a.dtype != b.dtype:
         raise refuse(kernel, f"mixed operand types {a.dtype} @ {b.dtype} have no tcgen05 kind",
-                     "convert one operand so both are bf16 or both f16", span=step.span)
-    if a.dtype.name not in ("bf16", "f16"):
-        raise refuse(kernel, f"{a.dtype} operands are not a 16-bit tensor-core kind",
-                     "use bf16 or f16 operands (block-scaled FP8 goes through krn_b200.ops.gemm_fp8_blockscaled)",
-                     span=step.span)
+                     "convert one operand so both are bf16, both f16, or both 8-bit floats", span=step.span)
+    elif a.dtype.name not in ("bf16", "f16"):
+        raise refuse(kernel, f"{a.dtype} operands are not a tensor-core kind",
+                     "use bf16, f16 or fp8 (f8e4m3fn / f8e5m2) operands; block-scaled FP8 goes through "
+                     "krn_b200.ops.matmul_fp8_blockscaled", span=step.span)
     output = kernel.tensor(store.tensor).dtype
     if output.name not in ("bf16", "f16", "f32"):
         raise refuse(kernel, f"{output} outputs are not supported", "store bf16, f16 or f32", span=store.span)
@@ -153,7 +159,11 @@ def _gemm(kernel: ir.Kernel) -> GemmPlan | None:
         raise refuse(kernel, f"a {kernel.tensor(bias).dtype} bias on a {output} result: the library epilogue reads the "
                              "bias in the type of the result", "declare bias and out with one element type",
                      span=store.span)
-    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step), transposed_b, bias, activation)
+    if a.dtype.name in fp8 and (bias is not None or activation is not None):
+        raise refuse(kernel, "the library epilogue (bias / activation) on an fp8 product has no prebuilt kernel",
+                     "store the product and apply the epilogue to 16-bit operands", span=store.span)
+    return GemmPlan(a.tensor, b.tensor, store.tensor, a.dtype, output, (bm, bn, loop.step), transposed_b, bias, activation,
+                    b.dtype if a.dtype.name in fp8 else None)
 
 
 def _head_index(e: ir.Expr) -> int | None:

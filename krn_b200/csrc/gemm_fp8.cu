@@ -37,8 +37,6 @@
 //    next block's scale early (the in-order warp then waits on that load in front of its fmas), scalar fmas.
 #include "gemm_common.cuh"
 
-#include <cstdlib>
-
 namespace krnb {
 namespace {
 
@@ -475,15 +473,7 @@ __global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitc
   }
 }
 
-int fp8_pair_mode(int64_t m) {
-  static int env = [] {
-    const char* v = getenv("KRN_B200_FP8_PAIR");
-    return v == nullptr ? -1 : atoi(v);
-  }();
-  if (env == 0) return 1;
-  if (env == 1) return 2;
-  return m > kBM ? 2 : 1;
-}
+int fp8_pair_mode(int64_t m) { return m > kBM ? 2 : 1; }
 
 }  // namespace
 }  // namespace krnb
@@ -533,8 +523,7 @@ static int fp8_product(int c_type, const void* a, const float* sa, const void* b
                 "TMA needs 16-byte aligned base addresses and row pitches (lda %lld, ldb %lld bytes, ldc %lld elements)",
                 (long long)lda, (long long)ldb, (long long)ldc);
   }
-  // CTA pairs whenever there is more than one 128-row panel (see the measurements at the top of this file);
-  // KRN_B200_FP8_PAIR=0/1 overrides for experiments
+  // CTA pairs whenever there is more than one 128-row panel (see the measurements at the top of this file)
   const int group = fp8_pair_mode(m);
   Problem p;
   p.m = int(m);

@@ -1,4 +1,5 @@
-// C[M,N] = A[M,K] * B[N,K]^T for 16-bit operands (bf16 / f16), f32 accumulation in tensor memory.
+// C[M,N] = A[M,K] * B[N,K]^T for 16-bit operands (bf16 / f16) and for unscaled 8-bit float pairs (e4m3 / e5m2, each
+// operand its own format), f32 accumulation in tensor memory.
 //
 // One persistent, warp-specialised kernel per CTA-pair mode:
 //   warp 0      TMA producer: one lane streams 128-byte-swizzled A and B tiles into a ring of shared-memory
@@ -21,8 +22,6 @@
 #include "gemm_common.cuh"
 
 #include <cuda_fp16.h>
-
-#include <cstdlib>
 
 namespace krnb {
 namespace {
@@ -66,10 +65,13 @@ __device__ __forceinline__ void fused_epilogue(uint32_t (&values)[32], const Epi
 template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ Destinations dst, Problem p, EpilogueSpec epilogue, uint32_t ab_format,
-               DeviceStatus* status) {
+               const __grid_constant__ Destinations dst, Problem p, EpilogueSpec epilogue, uint32_t a_format,
+               uint32_t b_format, DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kBK = kRowBytes / ELEM_BYTES;                 // K elements per stage
+  // b as (K, N): the stage holds [kBK rows of K] x [128 bytes of N] blocks, one per kBlockCols output columns
+  constexpr int kBlockCols = kRowBytes / ELEM_BYTES;
+  constexpr int kBlockBytes = kBK * kRowBytes;
   constexpr int kChunkCols = kRowBytes / int(sizeof(OutT));   // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
 
@@ -149,9 +151,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!p.b_kn) {
               tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
             } else {
-              // b is (K, N): 64-column x 64-row boxes, N contiguous; one box per 64 output columns
-              for (int blk = 0; blk < L::kBRows / 64; ++blk)
-                tma_load_2d(b_dst + blk * 8192, &map_b, row_b + blk * 64, kb * kBK, full_bar + 8 * stage);
+              // b is (K, N): boxes of 128 bytes of N x kBK rows of K, N contiguous; one box per kBlockCols columns
+              for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
+                tma_load_2d(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, full_bar + 8 * stage);
             }
           } else {
             // Both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both.
@@ -161,8 +163,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!p.b_kn) {
               tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
             } else {
-              for (int blk = 0; blk < L::kBRows / 64; ++blk)
-                tma_load_2d_pair(b_dst + blk * 8192, &map_b, row_b + blk * 64, kb * kBK, leader_full);
+              for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
+                tma_load_2d_pair(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, leader_full);
             }
           }
           if (++stage == L::kStages) {
@@ -175,16 +177,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc(ab_format, ab_format, kBM * CTA_GROUP, kBN, 0, p.b_kn ? 1u : 0u);
+      const uint32_t idesc = umma_idesc(a_format, b_format, kBM * CTA_GROUP, kBN, 0, p.b_kn ? 1u : 0u);
       // Descriptor words: b as (N, K) is K-major like a, 32 bytes of K per instruction inside the swizzle span; b as
-      // (K, N) is an MN-major operand, 64-column blocks 8192 bytes apart, 8-row K groups 1024 bytes apart, 16 K rows
-      // per instruction = 2048 bytes. Only the low word's start-address field moves (32-bit adds: this thread runs one
-      // instruction at a time).
+      // (K, N) is an MN-major operand: blocks of 128 bytes of N are kBlockBytes apart (8192 for 16-bit, 16384 for 8-bit
+      // elements), 8-row K groups 1024 bytes apart, and one instruction covers 32 bytes of K = 16 or 32 K rows of 128
+      // bytes. Only the low word's start-address field moves (32-bit adds: this thread runs one instruction at a time).
       const uint64_t a_desc0 = umma_desc_kmajor_sw128(stages_addr);
-      const uint64_t b_desc0 = p.b_kn ? umma_desc_mnmajor_sw128(stages_addr + L::kABytes, 8192, 1024)
+      const uint64_t b_desc0 = p.b_kn ? umma_desc_mnmajor_sw128(stages_addr + L::kABytes, kBlockBytes, 1024)
                                       : umma_desc_kmajor_sw128(stages_addr + L::kABytes);
       const uint32_t a_hi = uint32_t(a_desc0 >> 32), b_hi = uint32_t(b_desc0 >> 32);
-      const uint32_t b_step = p.b_kn ? uint32_t(2048 >> 4) : 2u;
+      const uint32_t b_step = p.b_kn ? uint32_t(((32 / ELEM_BYTES) * kRowBytes) >> 4) : 2u;
       uint32_t a_lo = uint32_t(a_desc0), b_lo = uint32_t(b_desc0);
       int stage = 0;
       uint32_t phase = 0;
@@ -338,11 +340,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
-           EpilogueSpec epilogue, uint32_t fmt, cudaStream_t stream) {
+           EpilogueSpec epilogue, uint32_t a_fmt, uint32_t b_fmt, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
-  auto kernel = gemm_tn_kernel<CTA_GROUP, 2, OutT, OUT_BF16>;
+  auto kernel = gemm_tn_kernel<CTA_GROUP, ELEM_BYTES, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / CTA_GROUP;
@@ -359,24 +361,42 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, epilogue, fmt, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, epilogue, a_fmt, b_fmt, ctx->status_dev));
   return KRN_B200_OK;
+}
+
+template <int ELEM_BYTES>
+int launch_for_output(const DeviceContext* ctx, int c_type, int group, const CUtensorMap& ma, const CUtensorMap& mb,
+                      const Destinations& mc, Problem p, EpilogueSpec epilogue, uint32_t a_fmt, uint32_t b_fmt,
+                      cudaStream_t stream) {
+  if (group == 2) {
+    if (c_type == KRN_B200_F32) return launch<2, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+    return launch<2, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+  }
+  if (c_type == KRN_B200_F32) return launch<1, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+  return launch<1, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
 }
 
 // Operands whose addresses or row pitches are not multiples of 16 bytes cannot be described to TMA. They take this
 // plain tiled kernel instead (64 x 64 outputs per block, 16 of K per step, f32 fma in k order — the same chain the
 // reference's scalar fallback runs, src/krn/compiler/emit.py:806-821). It exists so odd shapes such as the
 // reference's 50 x 38 x 70 example still run on the device; it is not a performance path.
-__device__ __forceinline__ float load_16bit(const uint16_t* p, bool bf16) {
-  const uint16_t w = *p;
-  if (bf16) return __uint_as_float(uint32_t(w) << 16);
-  return __half2float(__ushort_as_half(w));
+__device__ __forceinline__ float load_operand(const void* base, long long index, int type) {
+  if (type == KRN_B200_BF16) return __uint_as_float(uint32_t(static_cast<const uint16_t*>(base)[index]) << 16);
+  if (type == KRN_B200_F16) return __half2float(__ushort_as_half(static_cast<const uint16_t*>(base)[index]));
+  const uint32_t code = static_cast<const uint8_t*>(base)[index];
+  if (type == KRN_B200_E5M2) return __half2float(__ushort_as_half(uint16_t(code << 8)));  // upper byte of binary16
+  uint32_t pair;  // e4m3fn -> f16 is exact
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(uint16_t(code)));
+  return __half2float(__ushort_as_half(uint16_t(pair & 0xffffu)));
 }
 
 __global__ void __launch_bounds__(256)
-gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, void* __restrict__ c, int m,
-                         int n, int k, long long lda, long long ldb, long long ldc, bool in_bf16, int c_type, bool b_kn,
-                         EpilogueSpec epilogue) {
+gemm_tn_unaligned_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ c, int m,
+                         int n, int k, long long lda, long long ldb, long long ldc, int a_type, int b_type, int c_type,
+                         bool b_kn, EpilogueSpec epilogue) {
   __shared__ float as[16][65], bs[16][65];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
@@ -384,9 +404,9 @@ gemm_tn_unaligned_kernel(const uint16_t* __restrict__ a, const uint16_t* __restr
   for (int k0 = 0; k0 < k; k0 += 16) {
     for (int i = threadIdx.x; i < 64 * 16; i += 256) {
       const int r = i >> 4, kk = i & 15;
-      as[kk][r] = (row0 + r < m && k0 + kk < k) ? load_16bit(a + (long long)(row0 + r) * lda + k0 + kk, in_bf16) : 0.f;
+      as[kk][r] = (row0 + r < m && k0 + kk < k) ? load_operand(a, (long long)(row0 + r) * lda + k0 + kk, a_type) : 0.f;
       const long long b_at = b_kn ? (long long)(k0 + kk) * ldb + col0 + r : (long long)(col0 + r) * ldb + k0 + kk;
-      bs[kk][r] = (col0 + r < n && k0 + kk < k) ? load_16bit(b + b_at, in_bf16) : 0.f;
+      bs[kk][r] = (col0 + r < n && k0 + kk < k) ? load_operand(b, b_at, b_type) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -432,28 +452,27 @@ __global__ void zero_rows_kernel(uint8_t* c, long long row_bytes, long long pitc
 
 }  // namespace
 
-// Pair mode can be switched off for experiments (KRN_B200_GEMM_PAIR=0); by default it is used whenever
-// the problem has more than one 128-row panel.
-int gemm_pair_mode(int64_t m) {
-  static int env = [] {
-    const char* v = getenv("KRN_B200_GEMM_PAIR");
-    return v == nullptr ? -1 : atoi(v);
-  }();
-  if (env == 0) return 1;
-  if (env == 1) return 2;
-  return m > kBM ? 2 : 1;
-}
+// CTA pairs (256x256 tiles) whenever the problem has more than one 128-row panel; a single 128-row panel has
+// nothing for a second CTA to do.
+int gemm_pair_mode(int64_t m) { return m > kBM ? 2 : 1; }
 
 }  // namespace krnb
 
+static bool is_fp8(int type) { return type == KRN_B200_E4M3 || type == KRN_B200_E5M2; }
+static bool is_16bit(int type) { return type == KRN_B200_BF16 || type == KRN_B200_F16; }
+
 // Encode the operand and destination maps and launch the tile kernel: C_d[:, offset : offset + n] = A . B^T for every
-// destination d (each a row-major matrix of n_total columns with pitch ldc).
-static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type, const void* a, const void* b,
+// destination d (each a row-major matrix of n_total columns with pitch ldc). a_type / b_type are both 16-bit (and then
+// equal) or both 8-bit floats (each its own format).
+static int tiled_product(const krnb::DeviceContext* ctx, int a_type, int b_type, int c_type, const void* a, const void* b,
                          void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m,
                          int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream,
                          bool b_kn = false, krnb::EpilogueSpec epilogue = {nullptr, 0}) {
   using namespace krnb;
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  const bool fp8 = is_fp8(a_type);
+  const int ab_bytes = fp8 ? 1 : 2;
+  const uint32_t row_elements = uint32_t(128 / ab_bytes);  // elements in one 128-byte swizzle row
   Problem p;
   p.b_kn = b_kn ? 1 : 0;
   p.m = int(m);
@@ -462,24 +481,26 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
   p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
 
-  const CUtensorMapDataType ab_dt = ab_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType ab_dt = fp8                      ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                    : a_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap map_a, map_b;
   {
     uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
-    uint64_t strides[1] = {uint64_t(lda) * 2};
-    uint32_t box[2] = {64, uint32_t(kBM)};
+    uint64_t strides[1] = {uint64_t(lda) * ab_bytes};
+    uint32_t box[2] = {row_elements, uint32_t(kBM)};
     if (int rc = encode_tensor_map(&map_a, ab_dt, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
   }
   if (!b_kn) {
     uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
-    uint64_t strides[1] = {uint64_t(ldb) * 2};
-    uint32_t box[2] = {64, uint32_t(kBN / group)};
+    uint64_t strides[1] = {uint64_t(ldb) * ab_bytes};
+    uint32_t box[2] = {row_elements, uint32_t(kBN / group)};
     if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
   } else {
+    // one box = 128 bytes of N x one stage of K rows (64 for 16-bit, 128 for 8-bit elements)
     uint64_t dims[2] = {uint64_t(n), uint64_t(k)};
-    uint64_t strides[1] = {uint64_t(ldb) * 2};
-    uint32_t box[2] = {64, 64};
+    uint64_t strides[1] = {uint64_t(ldb) * ab_bytes};
+    uint32_t box[2] = {row_elements, row_elements};
     if (int rc = encode_tensor_map(&map_b, ab_dt, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
   }
   Destinations dst;
@@ -497,27 +518,26 @@ static int tiled_product(const krnb::DeviceContext* ctx, int ab_type, int c_type
     void* base = destinations[d < count ? d : 0];
     if (int rc = encode_tensor_map(&dst.maps[d], c_dt, 2, base, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  const uint32_t fmt = ab_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
-  if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+  if (fp8) {
+    const uint32_t a_fmt = a_type == KRN_B200_E4M3 ? kFmtE4M3 : kFmtE5M2;
+    const uint32_t b_fmt = b_type == KRN_B200_E4M3 ? kFmtE4M3 : kFmtE5M2;
+    return launch_for_output<1>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, a_fmt, b_fmt, stream);
   }
-  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
-  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, epilogue, fmt, stream);
+  const uint32_t fmt = a_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
+  return launch_for_output<2>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, fmt, fmt, stream);
 }
 
-// Argument checks, the K == 0 and unaligned cases and the launch, shared by the two layouts of b.
-static int product(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                   int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle, bool b_kn,
+// Argument checks, the K == 0 and unaligned cases and the launch, shared by the two layouts of b and by the 16-bit and
+// 8-bit operand kinds.
+static int product(int a_type, int b_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
+                   int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle, bool b_kn,
                    krnb::EpilogueSpec epilogue = {nullptr, 0}) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
-  if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
+  if (!((is_16bit(a_type) && a_type == b_type) || (is_fp8(a_type) && is_fp8(b_type)))) {
     return fail(KRN_B200_ERR_UNSUPPORTED,
-                "operand type %d is not available on sm_100a: this entry point multiplies 16-bit tiles. "
-                "Instead: pass KRN_B200_BF16 or KRN_B200_F16 (FP8 has its own entry point)", ab_type);
+                "operand types %d @ %d is not available on sm_100a: the tensor cores multiply two bf16, two f16 or two "
+                "8-bit float (e4m3 / e5m2) tiles. Instead: convert the operands to one of those pairs", a_type, b_type);
   }
   if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
     return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
@@ -532,6 +552,7 @@ static int product(int ab_type, int c_type, const void* a, const void* b, void* 
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  const int ab_bytes = is_fp8(a_type) ? 1 : 2;
   if (ldc < n || (k > 0 && (lda < k || ldb < (b_kn ? n : k)))) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row (lda %lld, ldb %lld, ldc %lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
@@ -546,36 +567,55 @@ static int product(int ab_type, int c_type, const void* a, const void* b, void* 
     KRNB_CUDA(cudaGetLastError());
     return KRN_B200_OK;
   }
-  if (k == 0 || !aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 ||
-      (ldc * c_bytes) % 16 != 0) {
+  if (k == 0 || !aligned16(a) || !aligned16(b) || !aligned16(c) || (lda * ab_bytes) % 16 != 0 ||
+      (ldb * ab_bytes) % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
     // not describable to TMA (or an epilogue over an empty sum): the plain tiled kernel, which needs element-aligned
     // addresses only and never touches a or b when K is 0
-    if ((k > 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 2 != 0) ||
+    if ((k > 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % ab_bytes != 0) ||
         reinterpret_cast<uintptr_t>(c) % c_bytes != 0) {
       return fail(KRN_B200_ERR_INVALID_ARGUMENT, "tensor addresses must be aligned to their element size");
     }
     const dim3 grid(unsigned((n + 63) / 64), unsigned((m + 63) / 64), 1);
-    gemm_tn_unaligned_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b),
-                                                       c, int(m), int(n), int(k), lda, ldb, ldc,
-                                                       ab_type == KRN_B200_BF16, c_type, b_kn, epilogue);
+    gemm_tn_unaligned_kernel<<<grid, 256, 0, stream>>>(a, b, c, int(m), int(n), int(k), lda, ldb, ldc, a_type, b_type,
+                                                       c_type, b_kn, epilogue);
     KRNB_CUDA(cudaGetLastError());
     return KRN_B200_OK;
   }
 
   const int group = gemm_pair_mode(m);
   void* destinations[1] = {c};
-  return tiled_product(ctx, ab_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream, b_kn,
-                       epilogue);
+  return tiled_product(ctx, a_type, b_type, c_type, a, b, destinations, 1, 0, n, m, n, k, lda, ldb, ldc, group, stream,
+                       b_kn, epilogue);
+}
+
+static int refuse_8bit(int ab_type) {
+  return krnb::fail(KRN_B200_ERR_UNSUPPORTED,
+                    "operand type %d is not available on sm_100a: this entry point multiplies 16-bit tiles. "
+                    "Instead: pass KRN_B200_BF16 or KRN_B200_F16 (8-bit float pairs go through krn_b200_gemm_fp8, "
+                    "block-scaled ones through krn_b200_gemm_fp8_blockscaled_tn)", ab_type);
+}
+
+extern "C" int krn_b200_gemm_fp8(int a_type, int b_type, int c_type, int b_kn, const void* a, const void* b, void* c,
+                                 int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                                 void* stream_handle) {
+  if (!is_fp8(a_type) || !is_fp8(b_type)) {
+    return krnb::fail(KRN_B200_ERR_UNSUPPORTED,
+                      "operand types %d @ %d is not available on sm_100a: this entry point multiplies 8-bit float "
+                      "tiles. Instead: pass KRN_B200_E4M3 or KRN_B200_E5M2 for each operand", a_type, b_type);
+  }
+  return product(a_type, b_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, b_kn != 0);
 }
 
 extern "C" int krn_b200_gemm_tn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
-  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, false);
+  if (!is_16bit(ab_type)) return refuse_8bit(ab_type);
+  return product(ab_type, ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, false);
 }
 
 extern "C" int krn_b200_gemm_nn(int ab_type, int c_type, const void* a, const void* b, void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, void* stream_handle) {
-  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, true);
+  if (!is_16bit(ab_type)) return refuse_8bit(ab_type);
+  return product(ab_type, ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, true);
 }
 
 extern "C" int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, const void* a, const void* b,
@@ -594,7 +634,9 @@ extern "C" int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, 
   if ((epilogue & kEpilogueBias) && reinterpret_cast<uintptr_t>(bias) % c_bytes != 0) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the bias vector must be aligned to the output element size");
   }
-  return product(ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, b_kn != 0, EpilogueSpec{bias, epilogue});
+  if (!is_16bit(ab_type)) return refuse_8bit(ab_type);
+  return product(ab_type, ab_type, c_type, a, b, c, m, n, k, lda, ldb, ldc, stream_handle, b_kn != 0,
+                 EpilogueSpec{bias, epilogue});
 }
 
 extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank,
@@ -638,6 +680,6 @@ extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, c
   DeviceContext* ctx = current_context();
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
-  return tiled_product(ctx, ab_type, c_type, a, b, destinations, ranks, rank * n_local, n_local * ranks, m, n_local, k, lda,
-                       ldb, ldc, gemm_pair_mode(m), stream);
+  return tiled_product(ctx, ab_type, ab_type, c_type, a, b, destinations, ranks, rank * n_local, n_local * ranks, m,
+                       n_local, k, lda, ldb, ldc, gemm_pair_mode(m), stream);
 }

@@ -10,7 +10,7 @@ from typing import Any
 from krn_b200.runtime import native
 
 _ELEMENT = {"bfloat16": native.BF16, "float16": native.F16, "float32": native.F32, "float8_e4m3fn": native.E4M3,
-            "uint8": native.E4M3}
+            "float8_e5m2": native.E5M2, "uint8": native.E4M3}
 
 
 def _type_of(tensor: Any) -> int:
@@ -68,6 +68,19 @@ def gemm_nn(a: Any, b: Any, c: Any, stream: Any = None) -> None:
         _type_of(a), _type_of(c), _pointer(a), _pointer(b), _pointer(c), m, n, k, _pitch(a), _pitch(b), _pitch(c),
         _stream(stream))
     native.check(status, "tile matrix product")
+
+
+def gemm_fp8(a: Any, b: Any, c: Any, *, b_kn: bool = False, stream: Any = None) -> None:
+    """c = a @ b for two 8-bit float tensors taken as stored (no scales): `b` is (N, K) — the operand of
+    `b.transpose()` — or, with `b_kn`, (K, N) row-major. Each operand is e4m3fn or e5m2 on its own; c bf16/f16/f32."""
+    (m, k) = a.shape
+    kb, n = (b.shape[0], b.shape[1]) if b_kn else (b.shape[1], b.shape[0])
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    status = native.library().krn_b200_gemm_fp8(
+        _type_of(a), _type_of(b), _type_of(c), int(b_kn), _pointer(a), _pointer(b), _pointer(c), m, n, k, _pitch(a),
+        _pitch(b), _pitch(c), _stream(stream))
+    native.check(status, "fp8 tile matrix product")
 
 
 def matmul(a: Any, b: Any, c: Any, *, b_kn: bool = True, epilogue: int = 0, bias: Any = None, stream: Any = None) -> None:

@@ -82,13 +82,14 @@ class DeviceTensor:
         storage words (uint16 / uint8), as the reference's tests handle bf16 (tests/compiler/test_tensor_cores.py:4)."""
         torch = _torch()
         data = self.data.detach().contiguous().cpu()
-        if self.element in (bf16, f8e4m3fn):
+        if self.element == bf16 or self.element.name in ("f8e4m3fn", "f8e5m2"):
             words = data.view(torch.int16 if self.element == bf16 else torch.uint8).numpy()
             words = words.view(np.uint16) if self.element == bf16 else words
             try:
                 import ml_dtypes
 
-                return words.view(ml_dtypes.bfloat16 if self.element == bf16 else ml_dtypes.float8_e4m3fn)
+                return words.view({"bf16": ml_dtypes.bfloat16, "f8e4m3fn": ml_dtypes.float8_e4m3fn,
+                                   "f8e5m2": ml_dtypes.float8_e5m2}[self.element.name])
             except ImportError:
                 return words
         return data.numpy()
@@ -225,12 +226,17 @@ class B200Launcher(api.Launcher):
         if a.shape[1] != b_k or tuple(c.shape) != (a.shape[0], b_n):
             raise ValueError(f"{captured.name}: shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, "
                              f"c {tuple(c.shape)}")
+        fp8 = plan.operand.name in ("f8e4m3fn", "f8e5m2")
+        operands = f"{plan.operand} @ {plan.operand_b}" if fp8 else f"{plan.operand} operands"
+        entry = ("krn_b200_gemm_fp8" if fp8 else "krn_b200_matmul" if plan.bias or plan.activation else
+                 f"krn_b200_gemm_{'tn' if plan.transposed_b else 'nn'}")
         explanation = api.Explanation(
-            captured.name, f"tile matrix product c = a @ b{'^T' if plan.transposed_b else ''}, {plan.operand} operands, "
+            captured.name, f"tile matrix product c = a @ b{'^T' if plan.transposed_b else ''}, {operands}, "
             f"{plan.output} output, declared tile {plan.tile}", launch or needed,
-            ("krn_b200_matmul" if plan.bias or plan.activation else
-             f"krn_b200_gemm_{'tn' if plan.transposed_b else 'nn'}") + " (tcgen05, 256x256 CTA-pair tiles)",
+            entry + " (tcgen05, 256x256 CTA-pair tiles)",
             ("the library chooses its own CTA tiling; the declared tile only shapes the inferred geometry",))
+        if fp8:
+            return Call(lambda stream: calls.gemm_fp8(a, b, c, b_kn=not plan.transposed_b, stream=stream.raw), explanation)
         if plan.bias is None and plan.activation is None:
             product = calls.gemm_tn if plan.transposed_b else calls.gemm_nn
             return Call(lambda stream: product(a, b, c, stream.raw), explanation)
@@ -378,6 +384,8 @@ class B200Device(api.Device):
             array, element = array.view(np.uint16), bf16
         elif name == "float8_e4m3fn":
             array, element = array.view(np.uint8), f8e4m3fn
+        elif name == "float8_e5m2":
+            array, element = array.view(np.uint8), BY_NAME["f8e5m2"]
         if array.dtype == np.uint16:
             tensor = torch.from_numpy(array.view(np.int16)).to(f"cuda:{self.ordinal}", non_blocking=True)
             tensor = tensor.view(torch.bfloat16) if element == bf16 else tensor.view(torch.uint16)
@@ -385,6 +393,8 @@ class B200Device(api.Device):
             tensor = torch.from_numpy(array).to(f"cuda:{self.ordinal}", non_blocking=True)
             if element == f8e4m3fn:
                 tensor = tensor.view(torch.float8_e4m3fn)
+            elif element is not None and element.name == "f8e5m2":
+                tensor = tensor.view(torch.float8_e5m2)
         return DeviceTensor(tensor, element)
 
     def launcher(self, kernel, launch=None) -> B200Launcher:

@@ -16,7 +16,7 @@ from krn_b200.hw.libraries import KERNEL_LIBRARY, Libraries
 
 ABI_VERSION = 1
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(6)
-F32, F16, BF16, E4M3 = range(4)
+F32, F16, BF16, E4M3, E5M2 = range(5)
 
 _i64, _int, _ptr, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 
@@ -25,6 +25,7 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
     "krn_b200_last_error": (ctypes.c_size_t, [ctypes.c_char_p, ctypes.c_size_t]),
     "krn_b200_device_status": (_int, [ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(ctypes.c_uint)]),
     "krn_b200_gemm_tn": (_int, [_int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "krn_b200_gemm_fp8": (_int, [_int, _int, _int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_copy_2d": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
     "krn_b200_matmul": (_int, [_int, _int, _int, _int, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_nn": (_int, [_int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),

@@ -29,6 +29,11 @@
 #define KRN_F16 1
 #define KRN_BF16 2
 #define KRN_E4M3 3
+#define KRN_E5M2 4
+/* An operand-type argument may name two types: the low byte is A's, bits 8..15 hold B's type + 1 (0 = same as A).
+ * The reference multiplies mixed e4m3 / e5m2 pairs (tests/compiler/test_tensor_cores.py:146,219-239). */
+#define KRN_A_TYPE(t) ((t) & 0xff)
+#define KRN_B_TYPE(t) ((((t) >> 8) & 0xff) ? (((t) >> 8) & 0xff) - 1 : ((t) & 0xff))
 
 /* ---- storage conversions ------------------------------------------------------------------------- */
 
@@ -110,11 +115,16 @@ void krn_oracle_bf16_round_array(const float* x, uint16_t* words, int64_t count)
   for (int64_t i = 0; i < count; ++i) words[i] = f32_to_bf16(x[i]);
 }
 
+/* e5m2 code -> value: IEEE-style, bias 15, all-ones exponent is inf / NaN (src/krn/data/formats.py:91) — the
+ * upper byte of the binary16 word with the same value. */
+static inline float e5m2_to_f32(uint8_t code) { return f16_to_f32((uint16_t)((uint16_t)code << 8)); }
+
 static inline float load_as_f32(const void* base, int type, int64_t index) {
   switch (type) {
     case KRN_F32: return ((const float*)base)[index];
     case KRN_F16: return f16_to_f32(((const uint16_t*)base)[index]);
     case KRN_BF16: return bf16_to_f32(((const uint16_t*)base)[index]);
+    case KRN_E5M2: return e5m2_to_f32(((const uint8_t*)base)[index]);
     default: return krn_oracle_e4m3_decode(((const uint8_t*)base)[index]);
   }
 }
@@ -168,6 +178,7 @@ void krn_oracle_matmul_epilogue(int c_type, const float* acc, const void* bias, 
 void krn_oracle_gemm_blocks(int ab_type, int c_type, int b_kn, const void* a, const void* b, void* c, int64_t m,
                             int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int bm, int bn, int bk,
                             int64_t row_begin, int64_t row_end) {
+  const int a_type = KRN_A_TYPE(ab_type), b_type = KRN_B_TYPE(ab_type);
   float* acc = aligned_alloc(64, ((size_t)bm * bn * 4 + 63) / 64 * 64);
   float* ta = aligned_alloc(64, ((size_t)bm * bk * 4 + 63) / 64 * 64);
   float* tb = aligned_alloc(64, ((size_t)bk * bn * 4 + 63) / 64 * 64);
@@ -181,13 +192,13 @@ void krn_oracle_gemm_blocks(int ab_type, int c_type, int b_kn, const void* a, co
         for (int i = 0; i < bm; ++i)
           for (int kk = 0; kk < bk; ++kk) {
             int64_t r = row0 + i, kc = k0 + kk;
-            ta[i * bk + kk] = (r < m && kc < k) ? load_as_f32(a, ab_type, r * lda + kc) : 0.0f;
+            ta[i * bk + kk] = (r < m && kc < k) ? load_as_f32(a, a_type, r * lda + kc) : 0.0f;
           }
         for (int kk = 0; kk < bk; ++kk)
           for (int j = 0; j < bn; ++j) {
             int64_t cidx = col0 + j, kc = k0 + kk;
             float v = 0.0f;
-            if (cidx < n && kc < k) v = b_kn ? load_as_f32(b, ab_type, kc * ldb + cidx) : load_as_f32(b, ab_type, cidx * ldb + kc);
+            if (cidx < n && kc < k) v = b_kn ? load_as_f32(b, b_type, kc * ldb + cidx) : load_as_f32(b, b_type, cidx * ldb + kc);
             tb[kk * bn + j] = v;
           }
         for (int i = 0; i < bm; ++i)
@@ -218,16 +229,17 @@ void krn_oracle_gemm_fast(int ab_type, int c_type, int b_kn, const void* a, cons
                           int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t row_begin,
                           int64_t row_end) {
   (void)m;
+  const int a_type = KRN_A_TYPE(ab_type), b_type = KRN_B_TYPE(ab_type);
   /* B as f32 [k][n] */
   float* bt = aligned_alloc(64, ((size_t)(k > 0 ? k : 1) * n * 4 + 63) / 64 * 64);
   float* row = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
   for (int64_t kk = 0; kk < k; ++kk)
     for (int64_t j = 0; j < n; ++j)
-      bt[kk * n + j] = b_kn ? load_as_f32(b, ab_type, kk * ldb + j) : load_as_f32(b, ab_type, j * ldb + kk);
+      bt[kk * n + j] = b_kn ? load_as_f32(b, b_type, kk * ldb + j) : load_as_f32(b, b_type, j * ldb + kk);
   for (int64_t i = row_begin; i < row_end; ++i) {
     for (int64_t j = 0; j < n; ++j) row[j] = 0.0f;
     for (int64_t kk = 0; kk < k; ++kk) {
-      float av = load_as_f32(a, ab_type, i * lda + kk);
+      float av = load_as_f32(a, a_type, i * lda + kk);
       const float* brow = bt + kk * n;
       for (int64_t j = 0; j < n; ++j) row[j] = __builtin_fmaf(av, brow[j], row[j]);
     }

@@ -19,7 +19,7 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-F32, F16, BF16, E4M3 = 0, 1, 2, 3
+F32, F16, BF16, E4M3, E5M2 = 0, 1, 2, 3, 4
 
 _LIB: ctypes.CDLL | None = None
 
@@ -113,20 +113,24 @@ def e4m3_decode(codes: np.ndarray) -> np.ndarray:
     return out
 
 
-_NUMPY = {F32: np.float32, F16: np.uint16, BF16: np.uint16, E4M3: np.uint8}
+_NUMPY = {F32: np.float32, F16: np.uint16, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8}
 
 
 # ---- tile product ---------------------------------------------------------------------------------------------
 
 
 def gemm(a: np.ndarray, b: np.ndarray, *, ab_type: int, c_type: int, b_kn: bool = False, tile: tuple[int, int, int] | None = None,
-         threads: int = 1) -> np.ndarray:
+         threads: int = 1, b_type: int | None = None) -> np.ndarray:
     """C = A @ B^T (b is (N, K)) or A @ B (b_kn, b is (K, N)): the k-ordered fma chain per element.
 
     With `tile=(bm, bn, bk)` the reference's loop structure runs (staged f32 tiles, block after block); without
     it the vectorised equivalent runs. Both give the same bits. Operands are storage words (uint16 for 16-bit
-    types, uint8 for e4m3, float32 for f32); the result is returned in storage words of `c_type`.
+    types, uint8 for e4m3 / e5m2, float32 for f32); the result is returned in storage words of `c_type`. `b_type`
+    names a different storage type for b (the reference multiplies mixed e4m3 / e5m2 pairs,
+    tests/compiler/test_tensor_cores.py:146,219-239).
     """
+    if b_type is not None:
+        ab_type = ab_type | ((b_type + 1) << 8)
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     m, k = a.shape
     n = b.shape[1] if b_kn else b.shape[0]

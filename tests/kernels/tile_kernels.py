@@ -170,6 +170,27 @@ def data_dependent_branch(a: Matrix[f32], c: Matrix[f32]) -> None:
 
 
 @kernel
+def fp8_pair_kn(a: Matrix[T.f8e4m3fn], b: Matrix[T.f8e5m2], c: Matrix[f32]) -> None:
+    """An fp8 pair loaded directly, b row-major as (K, N): the form of the reference's fp8 kernels
+    (tests/compiler/test_tensor_cores.py:47-78 with dtype / rhs fp8). The two operands have different formats."""
+    rows, cols = block.tile(32, 32)
+    acc = zeros(f32, 32, 32)
+    for ks in pipelined(a.shape[1], 32):
+        acc += a[rows, ks] @ b[ks, cols]
+    c[rows, cols] = acc
+
+
+@kernel
+def fp8_pair_nt(a: Matrix[T.f8e4m3fn], b: Matrix[T.f8e4m3fn], c: Matrix[bf16]) -> None:
+    """The same product with b stored (N, K): `a8[rows, ks] @ b8[cols, ks].transpose()`."""
+    rows, cols = block.tile(128, 128)
+    acc = zeros(f32, 128, 128)
+    for ks in pipelined(a.shape[1], 128):
+        acc += a[rows, ks] @ b[cols, ks].transpose()
+    c[rows, cols] = acc.to(bf16)
+
+
+@kernel
 def fp8_needs_direct_loads(a: Matrix[T.f8e4m3fn], b: Matrix[T.f8e4m3fn], c: Matrix[f32]) -> None:
     rows, cols = block.tile(32, 32)
     acc = zeros(f32, 32, 32)

@@ -66,6 +66,16 @@ def test_recognise_gemm_forms() -> None:
     assert "tile_kernels.py" in text and "^" in text  # compiler-style location with a caret
 
 
+def test_recognise_fp8_pairs() -> None:
+    """fp8 pairs that are direct tile loads are a product of their own, each operand in its own format
+    (src/krn/compiler/capture.py:3185-3192)."""
+    plan = recognise(capture(K.fp8_pair_kn.fn))
+    assert isinstance(plan, GemmPlan) and not plan.transposed_b
+    assert (plan.operand.name, plan.operand_b.name, plan.output.name) == ("f8e4m3fn", "f8e5m2", "f32")
+    plan = recognise(capture(K.fp8_pair_nt.fn))
+    assert plan.transposed_b and (plan.operand.name, plan.operand_b.name, plan.output.name) == ("f8e4m3fn", "f8e4m3fn", "bf16")
+
+
 def test_recognise_library_epilogues() -> None:
     """The reference's `matmul_epilogue` kernel (src/krn/lib/lib_kernels.py:30-48) under each flag set."""
     tile = (64, 64, 32)

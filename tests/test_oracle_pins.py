@@ -149,6 +149,8 @@ def fp8_table(exponent: int, mantissa: int) -> np.ndarray:
         value = (fraction / 2**mantissa * 2.0 ** (1 - bias)) if power == 0 else (1 + fraction / 2**mantissa) * 2.0 ** (power - bias)
         if exponent == 4 and code & 0x7F == 0x7F:
             value = np.nan
+        elif exponent == 5 and ((code >> mantissa) & 31) == 31:
+            value = np.nan if code & 3 else np.inf
         result[code] = -value if code & 128 else value
     return result
 
@@ -167,14 +169,18 @@ def test_e4m3_encode_matches_reference_encode() -> None:
     np.testing.assert_array_equal(o.e4m3_encode(golden["values"]), golden["codes"])
 
 
+@pytest.mark.parametrize("a_kind,b_kind", [("e4m3", "e4m3"), ("e4m3", "e5m2"), ("e5m2", "e4m3"), ("e5m2", "e5m2")])
 @pytest.mark.parametrize("m,n,k", [(50, 38, 70), (19, 7, 33), (65, 19, 0)])
-def test_fp8_codes_product_within_bound(m, n, k) -> None:
-    """Random e4m3 codes in [0,112)|sign from seed 81, unscaled product (tests/compiler/test_tensor_cores.py:219-239)."""
+def test_fp8_codes_product_within_bound(m, n, k, a_kind, b_kind) -> None:
+    """Random codes in [0,112)|sign from seed 81, unscaled product of every e4m3 / e5m2 pairing
+    (tests/compiler/test_tensor_cores.py:146,219-239), decoded with the test's own independent table."""
     rng = np.random.default_rng(81)
     raw = [rng.integers(0, 112, shape, dtype=np.uint8) | (rng.integers(0, 2, shape, dtype=np.uint8) << 7)
            for shape in ((m, k), (k, n))]
-    decoded = [fp8_table(4, 3)[x] for x in raw]
-    c = o.gemm(raw[0], raw[1], ab_type=o.E4M3, c_type=o.F32, b_kn=True, tile=(32, 32, 32))
+    tables = {"e4m3": fp8_table(4, 3), "e5m2": fp8_table(5, 2)}
+    kinds = {"e4m3": o.E4M3, "e5m2": o.E5M2}
+    decoded = [tables[a_kind][raw[0]], tables[b_kind][raw[1]]]
+    c = o.gemm(raw[0], raw[1], ab_type=kinds[a_kind], b_type=kinds[b_kind], c_type=o.F32, b_kn=True, tile=(32, 32, 32))
     agree(c, decoded[0], decoded[1], k, "f32")
 
 
