@@ -155,8 +155,9 @@ int krn_b200_device_status(int* code, int* site, unsigned int* block) {
   if (site != nullptr) *site = status->where;
   if (block != nullptr) *block = status->block;
   if (c != 0) {
-    krnb::fail(c, "device-side wait expired at site %d in block %u (info %u)", status->where, status->block,
-               status->info);
+    krnb::fail(c, c == KRN_B200_ERR_DEVICE_INDEX ? "index outside its tensor at site %d in block %u (value %u); the access was skipped"
+                                                 : "device-side wait expired at site %d in block %u (info %u)",
+               status->where, status->block, status->info);
     status->where = 0;
     status->block = 0;
     status->info = 0;

@@ -173,11 +173,11 @@ def attention_decode_fp8_paged(q: Any, k_pages: Any, v_pages: Any, page_table: A
                                v_scale: Any, o: Any, scale_log2: float, max_context: int, workspace: Any,
                                stream: Any = None) -> None:
     batch, hq, d = q.shape
-    _, page_size, hkv, _ = k_pages.shape
+    num_pages, page_size, hkv, _ = k_pages.shape
     nbytes = workspace.numel() * workspace.element_size() if hasattr(workspace, "numel") else workspace.nbytes
     status = native.library().krn_b200_attn_decode_fp8_paged(
         _pointer(q), _pointer(k_pages), _pointer(v_pages), _pointer(page_table), _pointer(context_len),
-        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, page_table.shape[1],
+        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, num_pages, page_table.shape[1],
         max_context, scale_log2, _pointer(workspace), nbytes, _stream(stream))
     native.check(status, "paged FP8 decode attention")
 
@@ -189,10 +189,10 @@ def attention_decode_fp8_paged_noalloc(q: Any, k_pages: Any, v_pages: Any, page_
     partials go to a 16 MiB array inside the kernel library). Calls on one device must not overlap on the GPU;
     make the first call on a device outside stream capture."""
     batch, hq, d = q.shape
-    _, page_size, hkv, _ = k_pages.shape
+    num_pages, page_size, hkv, _ = k_pages.shape
     status = native.library().krn_b200_attn_decode_fp8_paged_noalloc(
         _pointer(q), _pointer(k_pages), _pointer(v_pages), _pointer(page_table), _pointer(context_len),
-        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, page_table.shape[1],
+        _pointer(k_scale), _pointer(v_scale), _pointer(o), batch, hq, hkv, d, page_size, num_pages, page_table.shape[1],
         max_context, scale_log2, _stream(stream))
     native.check(status, "paged FP8 decode attention (built-in scratch)")
 

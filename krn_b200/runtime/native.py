@@ -14,8 +14,8 @@ from functools import cache
 from krn_b200.errors import CUDAError, TargetError
 from krn_b200.hw.libraries import KERNEL_LIBRARY, Libraries
 
-ABI_VERSION = 1
-OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(6)
+ABI_VERSION = 2
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT, ERR_DEVICE_INDEX = range(7)
 F32, F16, BF16, E4M3, E5M2 = range(5)
 
 _i64, _int, _ptr, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_float
@@ -41,10 +41,11 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
                ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _ptr]),
     "krn_b200_attn_decode_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "krn_b200_attn_decode_fp8_paged": (
-        _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32,
+        _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32,
                _ptr, _i64, _ptr]),
     "krn_b200_attn_decode_fp8_paged_noalloc": (
-        _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _ptr]),
+        _int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32,
+               _ptr]),
     "krn_b200_scatter_columns": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
 }
 
@@ -78,7 +79,8 @@ def check(status: int, feature: str) -> None:
         reason, _, instead = message.partition(" Instead: ")
         raise TargetError(feature, "sm_100a", reason.rstrip(". "), instead.rstrip(". ") or "use a supported shape and type")
     name = {ERR_INVALID_ARGUMENT: "KRN_B200_ERR_INVALID_ARGUMENT", ERR_CUDA: "KRN_B200_ERR_CUDA",
-            ERR_WORKSPACE: "KRN_B200_ERR_WORKSPACE", ERR_DEVICE_TIMEOUT: "KRN_B200_ERR_DEVICE_TIMEOUT"}.get(status, str(status))
+            ERR_WORKSPACE: "KRN_B200_ERR_WORKSPACE", ERR_DEVICE_TIMEOUT: "KRN_B200_ERR_DEVICE_TIMEOUT",
+            ERR_DEVICE_INDEX: "KRN_B200_ERR_DEVICE_INDEX"}.get(status, str(status))
     raise CUDAError(f"{name}: {message}")
 
 
@@ -91,6 +93,9 @@ def device_status() -> tuple[int, int, int]:
 
 def raise_device_status() -> None:
     code, site, block = device_status()
+    if code == ERR_DEVICE_INDEX:
+        raise CUDAError(f"KRN_B200_ERR_DEVICE_INDEX: a kernel met an index outside its tensor at site {site} in block "
+                        f"{block}; the access was skipped")
     if code != OK:
         name = "KRN_B200_ERR_DEVICE_TIMEOUT" if code == ERR_DEVICE_TIMEOUT else str(code)
         raise CUDAError(f"{name}: a bounded device-side wait expired at site {site} in block {block}")

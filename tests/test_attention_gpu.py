@@ -92,10 +92,8 @@ def test_config_four_shape_statistics(cuda) -> None:
     checked against float64, and every output row must be a convex combination of V rows (|o| <= max |v|)."""
     torch = cuda
     batch, hq, hkv, seq, d = 8, 32, 8, 4096, 128
-    gen = torch.Generator(device="cuda").manual_seed(3)
-    q = torch.randn((batch, hq, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
-    k = torch.randn((batch, hkv, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
-    v = torch.randn((batch, hkv, seq, d), device="cuda", generator=gen).to(torch.bfloat16)
+    words = o.config_attention(batch, hq, hkv, seq, d, seed=3)  # np.random.default_rng(3): Q, then K, then V
+    q, k, v = (torch.from_numpy(x.view(np.int16)).cuda().view(torch.bfloat16) for x in words)
     out = torch.empty_like(q)
     calls.attention_forward(q, k, v, out, math.log2(math.e) / math.sqrt(d), True)
     torch.cuda.synchronize()

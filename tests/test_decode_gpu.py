@@ -17,7 +17,7 @@ from krn_b200.runtime import calls
 pytestmark = pytest.mark.gpu
 
 
-def run(torch, q, kp, vp, table, lens, ks, vs):
+def run(torch, q, kp, vp, table, lens, ks, vs, max_context=None):
     d = q.shape[-1]
     dq = torch.from_numpy(q.view(np.int16)).cuda().view(torch.bfloat16)
     dk = torch.from_numpy(kp).cuda()
@@ -25,7 +25,7 @@ def run(torch, q, kp, vp, table, lens, ks, vs):
     dt, dl = torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda()
     dks, dvs = torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda()
     out = torch.full(dq.shape, float("nan"), device="cuda", dtype=torch.bfloat16)
-    max_context = int(table.shape[1]) * kp.shape[1]
+    max_context = max_context or int(table.shape[1]) * kp.shape[1]
     nbytes = calls.decode_workspace_bytes(q.shape[0], q.shape[1], d, max_context)
     workspace = torch.empty(nbytes, device="cuda", dtype=torch.uint8)
     calls.attention_decode_fp8_paged(dq, dk, dv, dt, dl, dks, dvs, out, math.log2(math.e) / math.sqrt(d), max_context,
@@ -63,6 +63,68 @@ def test_garbage_after_the_context_end_is_ignored(cuda) -> None:
     np.testing.assert_array_equal(clean, dirty)
 
 
+def test_context_lengths_are_clamped_to_max_context(cuda) -> None:
+    """A context_len beyond max_context (a caller bug, or a stale value) must not make the kernel read past the page
+    table row: it is clamped, so the result is that of the first max_context tokens. A negative one counts as 0."""
+    q, kp, vp, table, lens, ks, vs = o.config_decode(batch=4, q_heads=8, kv_heads=2, d=128, low=200, high=300, seed=9)
+    assert table.shape[1] == 5
+    max_context = 128  # two pages per sequence
+    narrow = np.ascontiguousarray(table[:, :2])
+    wild = lens.copy()
+    wild[1], wild[2], wild[3] = 1000, 2**30, -5
+    got = run(cuda, q, kp, vp, narrow, wild, ks, vs, max_context=max_context)
+    clamped = np.clip(wild, 0, max_context).astype(np.int32)
+    want = o.bf16_values(o.decode_fp8_paged(q, kp, vp, narrow, clamped, ks, vs,
+                                            scale_log2=math.log2(math.e) / math.sqrt(128)))
+    assert np.isfinite(got).all() and not got[3].any()  # the empty sequence's rows are zeros
+    assert o.rel_frobenius(got[:3], want[:3]) < 1e-2
+
+
+def test_page_ids_outside_the_pool_are_never_fetched(cuda) -> None:
+    """Ids of num_pages and -1: in table slots past the context they are not looked at; inside the context their keys
+    count as absent (the result equals that of the sequence without those 64 tokens) and the status word says so."""
+    from krn_b200.runtime import native
+
+    q, kp, vp, table, lens, ks, vs = o.config_decode(batch=3, q_heads=8, kv_heads=2, d=128, low=300, high=1400, seed=10)
+    scale = math.log2(math.e) / math.sqrt(128)
+    clean = run(cuda, q, kp, vp, table, lens, ks, vs)
+    unused = table.copy()
+    for b in range(3):
+        used = -(-int(lens[b]) // 64)
+        unused[b, used:] = kp.shape[0] if b % 2 else -1
+    np.testing.assert_array_equal(run(cuda, q, kp, vp, unused, lens, ks, vs), clean)
+    assert native.device_status()[0] == 0
+
+    # sequence 0 loses its third page, sequence 2 its first: full pages, so dropping them from the table and shortening
+    # the context by 64 describes the same set of keys
+    broken, repaired, shorter = table.copy(), table.copy(), lens.copy()
+    broken[0, 2], broken[2, 0] = kp.shape[0], -1
+    repaired[0, 2:-1], repaired[2, 0:-1] = table[0, 3:], table[2, 1:]
+    shorter[0] -= 64
+    shorter[2] -= 64
+    got = run(cuda, q, kp, vp, broken, lens, ks, vs)
+    code, site, _ = native.device_status()  # reads and clears the word
+    assert code == native.ERR_DEVICE_INDEX and site == 36
+    want = o.bf16_values(o.decode_fp8_paged(q, kp, vp, repaired, shorter, ks, vs, scale_log2=scale))
+    assert np.isfinite(got).all()
+    assert o.rel_frobenius(got, want) < 1e-2
+
+
+def test_config_five_as_configured(cuda) -> None:
+    """The benchmark configuration itself: 64 sequences, 32 / 8 heads, contexts U[1024, 8192] from seed 4, random page
+    table over a pool of ~4.6k pages — every sequence against the oracle, the shortest and the longest singled out."""
+    config = o.config_decode(batch=64, q_heads=32, kv_heads=8, d=128, low=1024, high=8192, page_size=64, seed=4)
+    lens = config[4]
+    got = run(cuda, *config)
+    want = o.bf16_values(o.decode_fp8_paged(*config, scale_log2=math.log2(math.e) / math.sqrt(128), threads=16))
+    assert np.isfinite(got).all()
+    assert o.rel_frobenius(got, want) < 1e-2
+    for b in (int(lens.argmin()), int(lens.argmax())):
+        assert o.rel_frobenius(got[b], want[b]) < 1e-2, (b, int(lens[b]))
+    worst = max(o.rel_frobenius(got[b], want[b]) for b in range(64))
+    assert worst < 3e-2, worst
+
+
 def test_refusals_and_workspace(cuda) -> None:
     torch = cuda
     q, kp, vp, table, lens, ks, vs = o.config_decode(batch=2, q_heads=4, kv_heads=1, d=128, low=10, high=100, seed=1)
@@ -72,4 +134,4 @@ def test_refusals_and_workspace(cuda) -> None:
     small = torch.empty(16, device="cuda", dtype=torch.uint8)
     with pytest.raises(Exception, match="KRN_B200_ERR_WORKSPACE"):
         calls.attention_decode_fp8_paged(*args, out, 1.0, int(table.shape[1]) * 64, small)
-    assert calls.decode_workspace_bytes(2, 4, 128, 128) == 2 * 4 * 1 * 130 * 4
+    assert calls.decode_workspace_bytes(2, 4, 128, 128) == (1088 + 1 + 2 * 4) * 4  # partials (64-word multiple) + counters

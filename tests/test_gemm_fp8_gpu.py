@@ -91,6 +91,49 @@ def test_k_zero_and_ragged_edges_leave_neighbours_alone(cuda) -> None:
     assert o.rel_frobenius(c[:33, :24].float().cpu().numpy(), want) < 1e-2
 
 
+def test_config_three_as_configured(cuda) -> None:
+    """The benchmark configuration itself: M = 8192, N = 28672, K = 8192 drawn with `np.random.default_rng(2)` (A, then
+    B), 1x128 / 128x128 absmax scales. 32 x 112 CTA-pair tiles over 64 K blocks is what the persistent scheduler and
+    the scale ring are built for and what small cases never reach. Sampled rows (first and last row of the first, middle
+    and last 256-row tiles, and tile-boundary neighbours) in the first, a middle and the last column tiles against the
+    oracle; the whole matrix through linearity, (sum_kb sa sb A8 B8^T) 1 = sum_kb sa (A8 (sb B8)^T 1)."""
+    torch = cuda
+    m, n, k = 8192, 28672, 8192
+    a_codes, sa, b_codes, sb = o.config_gemm_fp8(m, n, k, seed=2)
+    fp8 = torch.float8_e4m3fn
+    a, b = torch.from_numpy(a_codes).cuda().view(fp8), torch.from_numpy(b_codes).cuda().view(fp8)
+    dsa, dsb = torch.from_numpy(sa).cuda(), torch.from_numpy(sb).cuda()
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    calls.gemm_fp8_blockscaled_tn(a, dsa, b, dsb, c)
+    torch.cuda.synchronize()
+    rows = [0, 1, 127, 128, 255, 256, 257, 2047, 2048, 4095, 4096, 4351, 6143, 6144, 7935, 7936, 8063, 8191]
+    bands = [(0, 256), (256, 512), (14208, 14464), (n - 512, n - 256), (n - 256, n)]  # whole 256-column tiles
+    assert bool(torch.isfinite(c.float()).all())
+    for lo, hi in bands:
+        sub_b, sub_sb = b_codes[lo:hi], sb[lo // 128:hi // 128]
+        want = o.bf16_values(o.gemm_fp8_blockscaled(a_codes[rows], sa[rows], sub_b, sub_sb, threads=6))
+        got = c[rows, lo:hi].float().cpu().numpy()
+        assert o.rel_frobenius(got, want) < 1e-2, (lo, hi)
+        assert o.rel_frobenius(got, exact(a_codes[rows], sa[rows], sub_b, sub_sb)) < 3e-2, (lo, hi)  # the benchmark's tolerance
+    # linearity over the whole matrix, in float64 on the device
+    ones = torch.ones((n, 1), device="cuda", dtype=torch.float64)
+    weights = torch.zeros((k,), device="cuda", dtype=torch.float64)
+    for lo in range(0, n, 4096):  # sum_n sb[n // 128, k // 128] * B8[n, k], in slabs to bound the f64 temporaries
+        hi = min(n, lo + 4096)
+        scales = dsb[lo // 128:hi // 128].double().repeat_interleave(128, 0).repeat_interleave(128, 1)
+        weights += (b[lo:hi].double() * scales).sum(0)
+    rhs = (a.double() * dsa.double().repeat_interleave(128, 1)) @ weights[:, None]
+    assert float((c.double() @ ones - rhs).norm() / rhs.norm()) < 5e-3
+    del c
+    c32 = torch.empty((m, n), device="cuda", dtype=torch.float32)
+    calls.gemm_fp8_blockscaled_tn(a, dsa, b, dsb, c32)
+    torch.cuda.synchronize()
+    assert float((c32.double() @ ones - rhs).norm() / rhs.norm()) < 1e-5
+    for lo, hi in bands:
+        want32 = o.gemm_fp8_blockscaled(a_codes[rows], sa[rows], b_codes[lo:hi], sb[lo // 128:hi // 128], c_type=o.F32, threads=6)
+        assert o.rel_frobenius(c32[rows, lo:hi].cpu().numpy(), want32) < 1e-5, (lo, hi)
+
+
 def test_column_sharded_fp8_product_stores_into_every_destination(cuda) -> None:
     """The sharded entry point on one GPU: two "ranks" are two launches, each storing its column block into both
     destination buffers; both copies must equal the unsharded product bit for bit."""

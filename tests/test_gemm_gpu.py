@@ -190,16 +190,13 @@ def test_config_two_statistics_at_full_size(cuda) -> None:
     (A @ B^T @ 1 = A @ (B^T @ 1)) and against the relative Frobenius tolerance 1e-2."""
     torch = cuda
     size = 8192
-    gen = torch.Generator(device="cuda").manual_seed(1)
-    a = torch.randn((size, size), device="cuda", generator=gen).to(torch.bfloat16)
-    b = torch.randn((size, size), device="cuda", generator=gen).to(torch.bfloat16)
+    a_words, b_words = o.config_gemm_bf16(size, size, size, seed=1)  # np.random.default_rng(1): A, then B
+    a, b = to_device(torch, a_words, "bf16"), to_device(torch, b_words, "bf16")
     c = torch.empty((size, size), device="cuda", dtype=torch.bfloat16)
     calls.gemm_tn(a, b, c)
     torch.cuda.synchronize()
     rows = [0, 1, 127, 128, 4095, 4096, 8064, 8191]
-    aw = a[rows].view(torch.int16).cpu().numpy().view(np.uint16)
-    bw = b.view(torch.int16).cpu().numpy().view(np.uint16)
-    want = o.bf16_values(o.gemm(aw, bw, ab_type=o.BF16, c_type=o.BF16, threads=8))
+    want = o.bf16_values(o.gemm(a_words[rows], b_words, ab_type=o.BF16, c_type=o.BF16, threads=8))
     got = o.bf16_values(c[rows].view(torch.int16).cpu().numpy().view(np.uint16))
     assert o.rel_frobenius(got, want) < 1e-2
     assert np.mean(got.view(np.uint32) == want.view(np.uint32)) > 0.95  # same bf16 word almost everywhere
