@@ -2,30 +2,40 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-Default workload (N = 1): the bf16 tile product C = A @ B^T with M = N = K = 8192, f32 accumulation, bf16
-output — the configuration the headline metric is quoted on. A "step" is one pass of the hot path over one
-batch of synthetic operands (seeded N(0,1)). The other workloads measure the other configurations with the same
-harness: `gemm_fp8` (block-scaled e4m3, 8192 x 28672 x 8192), `attn_fwd` (causal GQA flash attention, B=8, Hq=32,
-Hkv=8, S=4096, D=128), `attn_decode` (paged FP8 decode, 64 sequences, contexts 1024..8192).
+Headline workload: the bf16 tile product C = A @ B^T with M = N = K = 8192, f32 accumulation, bf16 output — the
+configuration the headline metric is quoted on. A "step" is one pass of the hot path over one batch of synthetic
+operands (seeded N(0,1), generated on the device). With the default `--workload all` the line also carries
+`workloads`: one sub-record with the same keys for each of the other configurations — `gemm_fp8` (block-scaled e4m3,
+8192 x 28672 x 8192), `attn_fwd` (causal GQA flash attention, B=8, Hq=32, Hkv=8, S=4096, D=128), `attn_decode` (paged
+FP8 decode, 64 sequences, contexts 1024..8192). `--workload NAME` measures that one alone as the headline.
 
-Keys of the line:
-  value         whole-job throughput with operands resident in HBM (CUDA events on the launching stream, max over ranks)
+Timing: W (at least 3) warm-up steps, then TRIALS of exactly K steps each, every trial bracketed by a barrier and a
+synchronisation on both sides and timed with CUDA events on the launching stream, max over ranks; as many trials (at
+least 5) as it takes for them to last about a second together, so that the nvidia-smi clock samples in `clocks` fall
+INSIDE the timed region. `ms_per_step` is the median over trials of (trial time / K); min and max are in `timing`.
+
+Keys of the line (and of each sub-record):
+  value         whole-job throughput with operands resident in HBM
   e2e           the same metric through the public host-operand API (krn_b200.streaming) with HOST buffers: every step
                 copies the operands from pinned host memory, runs the kernels and reads the result back, all inside the
                 timed region (panels of the copies overlap the kernels)
-  roofline      achieved vs measured peak for the dominant kernel (algorithmic FLOPs or bytes / event time)
-  cpu_baseline  the CPU restatement of the reference's C backend timed on this machine's cores on a bounded sample
+  roofline      achieved vs measured peak for the dominant kernel (algorithmic FLOPs or bytes / event time); `frac` is
+                against the burst cuBLAS figure, `frac_of_sustained_peak` against the seconds-long one
+  rel_frobenius the kernel's output on a sample of the workload against the CPU oracle on the same operands
+  cpu_baseline  the CPU restatement of the reference's C backend timed on this machine's cores on a bounded sample,
+                on all cores and (`one_thread`) on one, which is how the reference itself runs a kernel call
   clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) total work is fixed ("strong" scaling): the tile
 products are sharded by output column blocks and every rank ends with the whole row-major C — the all-gather of the
-column blocks is done by the product kernel's own epilogue (TMA stores into every rank's C over NVLink, then a device
-barrier; KRN_B200_GATHER=nccl selects an NCCL all-gather + re-layout kernel instead); attention is sharded by (batch,
-kv head) and decode by sequence, with no collective. The end-to-end leg of the products copies `a` once per node (each
-rank its share of the rows, all-gathered over NVLink).
+column blocks and the cross-rank completion are done by the product kernel itself (TMA stores into every rank's C over
+NVLink; the last CTA exchanges flags with the peers; KRN_B200_GATHER=nccl selects an NCCL all-gather + re-layout kernel
+instead); attention is sharded by (batch, kv head) and decode by sequence, with no collective. The end-to-end leg of
+the products copies `a` once per node (each rank its share of the rows, all-gathered over NVLink).
 
 `--impl reference` times the reference's CPU implementation of the path (its C backend restated in oracle/, since
-the reference itself needs Python 3.14 + clang and holds no C sources) on the host cores, rank 0 only.
+the reference itself needs Python 3.14 + clang and holds no C sources) on the host cores, rank 0 only; each step is a
+bounded sample whose extents are in `config.sample`.
 """
 
 from __future__ import annotations
@@ -49,7 +59,7 @@ if str(ROOT) not in sys.path:
 # gemm_bf16 / gemm_fp8 / attn_fwd: captured on a smaller case (see profiles/) and scaled to the full launch by the
 # algorithmic bytes, which DRAM traffic follows for these streaming operand/output patterns; attn_decode: captured on
 # the bench workload itself.
-NCU_TRAFFIC_BYTES = {"gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(340.0e6 * 773.9 / 193.5),
+NCU_TRAFFIC_BYTES = {"gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(220.3e6 * 773.9 / 193.5),
                      "attn_fwd": int(137.6e6 * 671.1 / 167.8), "attn_decode": int(690.2e6)}
 
 
@@ -111,6 +121,8 @@ class Workload:
     name = metric = dtype = description = ""
     unit, bound = "TFLOP/s", "tensor"
     launches_per_step = 1
+    reference_columns = 1024     # extent that bounds the CPU sample of `--impl reference` (columns, or sequence length)
+    single_thread_columns = 512  # the same for the faithful one-thread CPU sample
 
     def __init__(self, torch, rank: int, world: int, size: list[int] | None = None) -> None:
         self.torch, self.rank, self.world = torch, rank, world
@@ -165,12 +177,13 @@ class GemmBf16(Workload):
             else:
                 self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
                 self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
-            self.launches_per_step = 2
+                self.launches_per_step = 2
 
     @property
     def config(self) -> dict:
-        gather = ("all-gather of the output columns fused into the product kernel (TMA stores into every rank's C over "
-                  "NVLink) + device barrier" if self.fused else "NCCL all-gather of the output columns + re-layout kernel")
+        gather = ("all-gather of the output columns and the cross-rank completion fused into the product kernel (TMA "
+                  "stores into every rank's C over NVLink, flags exchanged by the last CTA)" if self.fused
+                  else "NCCL all-gather of the output columns + re-layout kernel")
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
                 "sharding": f"N-column blocks x{self.world}, {gather}" if self.world > 1 else "one GPU, no exchange",
                 "l2": self.l2_note("operands and output", 2 * (self.m * self.k + self.n_local * self.k + self.m * (
@@ -215,6 +228,21 @@ class GemmBf16(Workload):
     def e2e_step(self, calls) -> None:
         self.streamed.run(self.host_in[0], self.host_in[1], self.host_out)
 
+    def parity_sample(self, oracle, calls) -> dict:
+        """Relative Frobenius error of sampled output rows against the CPU oracle on the same operands."""
+        import numpy as np
+
+        torch = self.torch
+        self.kernel_only(calls)
+        torch.cuda.synchronize()
+        rows = [0, 1, 127, 128, self.m // 2 - 1, self.m // 2, self.m - 129, self.m - 1]
+        words = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        want = oracle.bf16_values(oracle.gemm(words(self.a[rows]), words(self.b), ab_type=oracle.BF16, c_type=oracle.BF16,
+                                              threads=8))
+        got = oracle.bf16_values(words(self.c_local[rows]))
+        return {"value": oracle.rel_frobenius(got, want), "tolerance": 1e-2,
+                "sample": f"{len(rows)} rows x all {self.n_local} columns against the oracle's k-ordered fma chain"}
+
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         """The faithful block loop (128x128x32 tiles) on the first `cores` block rows of the same problem, one
         block row per thread; `columns` restricts N to bound the time. Returns (work, description, callable)."""
@@ -257,7 +285,7 @@ class GemmFp8(Workload):
             else:
                 self.slabs = torch.empty((world, self.m, self.n_local), device="cuda", dtype=torch.bfloat16)
                 self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
-            self.launches_per_step = 2
+                self.launches_per_step = 2
 
     def _quantize(self, x, block_rows: int):
         """Codes with each block's absmax mapped to 448 (scale = absmax / 448), blocks of block_rows x 128."""
@@ -273,8 +301,9 @@ class GemmFp8(Workload):
     def config(self) -> dict:
         return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k,
                 "sharding": (f"N-column blocks x{self.world}, " + (
-                    "all-gather of the output columns fused into the product kernel (TMA stores into every rank's C over "
-                    "NVLink) + device barrier" if self.fused else "NCCL all-gather of the output columns + re-layout kernel"))
+                    "all-gather of the output columns and the cross-rank completion fused into the product kernel (TMA "
+                    "stores into every rank's C over NVLink, flags exchanged by the last CTA)" if self.fused
+                    else "NCCL all-gather of the output columns + re-layout kernel"))
                 if self.world > 1 else "one GPU, no exchange",
                 "l2": self.l2_note("operands and output", self.m * self.k + self.n_local * self.k + 2 * self.m * (
                     self.n if self.world > 1 else self.n_local), 1)}
@@ -321,6 +350,24 @@ class GemmFp8(Workload):
 
     def e2e_step(self, calls) -> None:
         self.streamed.run(*self.host_in, self.host_out)
+
+    def parity_sample(self, oracle, calls) -> dict:
+        import numpy as np
+
+        torch = self.torch
+        self.kernel_only(calls)
+        torch.cuda.synchronize()
+        rows = [0, 1, 127, 128, 255, 256, self.m // 2, self.m - 257, self.m - 256, self.m - 1]
+        host = lambda t: t.contiguous().view(torch.uint8).cpu().numpy() if t.dtype == torch.float8_e4m3fn else t.cpu().numpy()
+        errors = []
+        for lo in (0, (self.n_local // 2) // 256 * 256, self.n_local - 256):  # first, a middle and the last 256-column tile
+            want = oracle.bf16_values(oracle.gemm_fp8_blockscaled(
+                host(self.a[rows]), host(self.sa[rows]), host(self.b[lo:lo + 256]), host(self.sb[lo // 128:lo // 128 + 2]),
+                threads=8))
+            got = oracle.bf16_values(self.c_local[rows, lo:lo + 256].contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+            errors.append(oracle.rel_frobenius(got, want))
+        return {"value": max(errors), "tolerance": 3e-2,
+                "sample": f"{len(rows)} rows x the first, a middle and the last 256-column tile against the oracle"}
 
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         n = columns or 2048
@@ -399,6 +446,25 @@ class AttnFwd(Workload):
         if self.batch_local:
             self.streamed.run(*self.host_in, self.host_out, self.scale_log2, True)
 
+    def parity_sample(self, oracle, calls) -> dict:
+        """Causal attention of the first 1024 queries depends on the first 1024 keys only, so that prefix of four q heads
+        (one kv head) is checked against the oracle's statement-by-statement attention on the same prefix."""
+        import numpy as np
+
+        torch = self.torch
+        q, k, v, o = self.sets[0]
+        self.run(calls, self.sets[0])
+        torch.cuda.synchronize()
+        rows = min(1024, self.seq)
+        words = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        group = self.hq // self.hkv
+        want = oracle.bf16_values(oracle.flash_attention(words(q[:1, :group, :rows]), words(k[:1, :1, :rows]),
+                                                         words(v[:1, :1, :rows]), dtype=oracle.BF16, scale=self.scale_log2,
+                                                         causal=True, bq=64, bk=64, threads=group))
+        got = oracle.bf16_values(words(o[:1, :group, :rows]))
+        return {"value": oracle.rel_frobenius(got, want), "tolerance": 1e-2,
+                "sample": f"the first {rows} query rows of {group} q heads (batch 0, kv head 0) against the oracle"}
+
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         heads = cores
         seq = columns or 2048
@@ -418,7 +484,7 @@ class AttnDecode(Workload):
     unit, bound = "GB/s", "hbm"
     description = "FP8 e4m3 paged decode attention B=64 Hq=32 Hkv=8 D=128, contexts U[1024,8192], page 64 (seed 4)"
     batch, hq, hkv, d, page = 64, 32, 8, 128, 64
-    launches_per_step = 2
+    launches_per_step = 1  # one kernel (a memset node of the counters precedes it)
 
     def __init__(self, torch, rank, world, size=None) -> None:
         super().__init__(torch, rank, world)
@@ -501,6 +567,22 @@ class AttnDecode(Workload):
         self.step(calls)
         self.host_out.copy_(self.o, non_blocking=True)
 
+    def parity_sample(self, oracle, calls) -> dict:
+        import numpy as np
+
+        torch = self.torch
+        k_pages, v_pages = self.pools[0]
+        calls.attention_decode_fp8_paged(self.q, k_pages, v_pages, self.table, self.lens, self.k_scale, self.v_scale, self.o,
+                                         self.scale_log2, 8192, self.workspace, torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        words = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        codes = lambda t: t.view(torch.uint8).cpu().numpy()
+        want = oracle.bf16_values(oracle.decode_fp8_paged(
+            words(self.q), codes(k_pages), codes(v_pages), self.table.cpu().numpy(), self.lens.cpu().numpy(),
+            self.k_scale.cpu().numpy(), self.v_scale.cpu().numpy(), scale_log2=self.scale_log2, threads=8))
+        return {"value": oracle.rel_frobenius(oracle.bf16_values(words(self.o)), want), "tolerance": 3e-2,
+                "sample": f"all {self.local} sequences against the oracle"}
+
     def cpu_sample(self, oracle, cores: int, columns: int | None = None):
         config = oracle.config_decode(batch=cores, q_heads=self.hq, kv_heads=self.hkv, d=self.d, low=1024, high=2048, seed=4)
         tokens = int(config[4].sum())
@@ -514,37 +596,170 @@ class AttnDecode(Workload):
 WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, AttnFwd, AttnDecode)}
 
 
+def cpu_rates(workload, oracle, cores: int, columns: int | None, repeats: int = 1) -> dict:
+    """The CPU restatement of the reference's C backend on a bounded sample of the workload: once on `cores` threads (the
+    grid split over threads, the way the reference gets concurrency across streams) and once on ONE thread, which is
+    how the reference runs a single kernel call (src/krn/runtime/cpu.py:137-140)."""
+    work, sample, run = workload.cpu_sample(oracle, cores, columns)
+    start = time.perf_counter()
+    for _ in range(repeats):
+        run()
+    seconds = (time.perf_counter() - start) / repeats
+    work1, sample1, run1 = workload.cpu_sample(oracle, 1, workload.single_thread_columns)
+    start = time.perf_counter()
+    run1()
+    seconds1 = time.perf_counter() - start
+    return {"value": workload.scale(work, seconds * 1e3), "unit": workload.unit, "cores": cores, "kind": "port",
+            "sample": sample, "seconds": seconds,
+            "one_thread": {"value": workload.scale(work1, seconds1 * 1e3), "unit": workload.unit, "cores": 1,
+                           "sample": sample1, "seconds": seconds1}}
+
+
 def reference_arm(args, rank: int) -> int:
-    """The reference's CPU implementation of the path (restated C backend) on the host cores; rank 0 only."""
+    """The reference's CPU implementation of the path (restated C backend) on the host cores; rank 0 only. Each step is a
+    bounded sample of the workload (its extents are in `config.sample`); the value is the sample's rate."""
     if rank != 0:
         return 0
     from oracle import oracle
 
     cores = min(os.cpu_count() or 1, 64)
-    kind = WORKLOADS[args.workload]
+    kind = WORKLOADS[args.workload if args.workload != "all" else "gemm_bf16"]
     workload = kind.__new__(kind)
     workload.world, workload.scale_log2 = 1, math.log2(math.e) / math.sqrt(128)
-    work, sample, run = workload.cpu_sample(oracle, cores, columns=1024)
-    warmup = min(args.warmup, 1)
-    for _ in range(warmup):
+    work, sample, run = workload.cpu_sample(oracle, cores, columns=kind.reference_columns)
+    for _ in range(args.warmup):
         run()
     start = time.perf_counter()
     for _ in range(args.steps):
         run()
     seconds = time.perf_counter() - start
     value = workload.scale(work * args.steps, seconds * 1e3)
+    work1, sample1, run1 = workload.cpu_sample(oracle, 1, kind.single_thread_columns)
+    start = time.perf_counter()
+    run1()
+    seconds1 = time.perf_counter() - start
     line = {
         "impl": "reference", "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic",
-        "config": {"workload": workload.description,
-                   **{key: getattr(kind, key) for key in ("m", "n", "k") if hasattr(kind, key)}},
-        "cpu_baseline": {"value": value, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload.description, "sample": sample,
+                   "note": "each step runs the sample, not the full problem; value is the sample's rate"},
+        "cpu_baseline": {"value": value, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample,
+                         "one_thread": {"value": workload.scale(work1, seconds1 * 1e3), "unit": workload.unit, "cores": 1,
+                                        "sample": sample1, "seconds": seconds1}},
         "e2e": {"value": value, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
     return 0
+
+
+class Harness:
+    """Timing of one workload: device events around `steps` calls, several trials, the median; max over ranks."""
+
+    def __init__(self, torch, args, rank: int, world: int, local_rank: int) -> None:
+        self.torch, self.args, self.rank, self.world, self.local_rank = torch, args, rank, world, local_rank
+        self.distributed = world > 1
+        self.peaks, self.peak_kind = measured_peaks()
+
+    def barrier(self) -> None:
+        if self.distributed:
+            self.torch.distributed.barrier()
+        self.torch.cuda.synchronize()
+
+    def trial(self, fn, steps: int) -> float:
+        """Milliseconds for `steps` calls of fn, on the device, max over ranks."""
+        torch = self.torch
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        self.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device="cuda", dtype=torch.float64)
+        if self.distributed:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        return float(ms.item())
+
+    def trials(self, fn, steps: int, budget_ms: float, least: int = 5, most: int = 400) -> list[float]:
+        """Per-step milliseconds of each of several trials of `steps` calls: at least `least` trials and as many as it
+        takes for the trials together to last `budget_ms` (every rank runs the same number: rank 0 decides)."""
+        torch = self.torch
+        first = self.trial(fn, steps)
+        count = max(least - 1, min(most, int(math.ceil(budget_ms / max(first, 1e-3))) - 1))
+        if self.distributed:
+            agreed = torch.tensor([count], device="cuda")
+            torch.distributed.broadcast(agreed, 0)
+            count = int(agreed.item())
+        return [first / steps] + [self.trial(fn, steps) / steps for _ in range(count)]
+
+    def measure(self, workload, calls, native, *, e2e: bool, cpu: bool, check: bool) -> dict:
+        args, torch = self.args, self.torch
+        warmup = max(args.warmup, 3)
+        for _ in range(warmup):
+            workload.step(calls)
+        torch.cuda.synchronize()
+        # ---- resident-operand throughput: the clock sampler runs for the whole timed region (>= 1 s of launches)
+        with ClockSampler(self.local_rank) as sampler:
+            per_step = self.trials(lambda: workload.step(calls), args.steps, args.region_ms)
+        clocks = sampler.summary()
+        native.raise_device_status()
+        per_step.sort()
+        ms_per_step = per_step[len(per_step) // 2]
+        value = workload.scale(workload.work(), ms_per_step)
+
+        # ---- the dominant kernel alone (roofline)
+        kernel = self.trials(lambda: workload.kernel_only(calls), args.steps, args.region_ms / 4)
+        kernel.sort()
+        kernel_ms = kernel[len(kernel) // 2]
+        achieved = workload.scale(workload.kernel_work(), kernel_ms)
+        peak, peak_note = workload.peak(self.peaks)
+        roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit,
+                    "frac": achieved / peak,
+                    "traffic": None if args.size or self.world > 1 else NCU_TRAFFIC_BYTES[workload.name],
+                    "peak_kind": f"{self.peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
+        if workload.bound == "tensor":
+            factor = 2.0 if workload.dtype.startswith("fp8") else 1.0
+            sustained = factor * self.peaks["bf16_tflops_sustained"]
+            roofline["frac_of_sustained_peak"] = achieved / sustained
+            roofline["applies"] = ("sustained: the timed region is a seconds-long run of back-to-back launches under the "
+                                   "power cap; `frac` (burst denominator) is the stricter figure and is the one reported")
+            roofline["frac_of_nominal_dense_peak"] = achieved / (4500.0 if factor == 2.0 else 2250.0)
+
+        record = {"metric": workload.metric, "value": value, "unit": workload.unit, "ms_per_step": ms_per_step,
+                  "trials": len(per_step), "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1],
+                  "dtype": workload.dtype, "config": workload.config, "roofline": roofline, "clocks": clocks,
+                  "gpu_launches": workload.launches_per_step * args.steps * len(per_step)}
+
+        # ---- end to end with host buffers
+        if e2e:
+            try:
+                h2d, d2h = workload.host_buffers()
+                for _ in range(2):
+                    workload.e2e_step(calls)
+                e2e_steps = max(3, min(args.steps, 10))
+                e2e_ms = sorted(self.trial(lambda: workload.e2e_step(calls), e2e_steps) / e2e_steps for _ in range(3))[1]
+                record["e2e"] = {"value": workload.scale(workload.work(), e2e_ms), "unit": workload.unit,
+                                 "h2d_bytes_per_step": h2d * self.world, "d2h_bytes_per_step": d2h * self.world,
+                                 "ms_per_step": e2e_ms}
+                native.raise_device_status()
+            except Exception as error:  # the device-resident numbers stand on their own; say why this leg is absent
+                record["e2e"] = None
+                record["e2e_error"] = f"{type(error).__name__}: {error}"
+        else:
+            record["e2e"] = None
+
+        # ---- parity on a sample and the CPU baseline (rank 0, N = 1 only)
+        if self.rank == 0 and self.world == 1 and (check or cpu):
+            from oracle import oracle
+
+            if check:
+                record["rel_frobenius"] = workload.parity_sample(oracle, calls)
+            if cpu:
+                record["cpu_baseline"] = cpu_rates(workload, oracle, min(os.cpu_count() or 1, 64), None)
+        record.setdefault("cpu_baseline", None)
+        return record
 
 
 def main() -> int:
@@ -553,10 +768,13 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="gemm_bf16", choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default="all", choices=["all", *sorted(WORKLOADS)],
+                        help="all: the headline workload (gemm_bf16) plus a sub-record for each of the others")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--kernel-only", action="store_true", help="profiling: skip the e2e and CPU legs")
+    parser.add_argument("--kernel-only", action="store_true", help="profiling: skip the e2e, parity and CPU legs")
     parser.add_argument("--size", type=int, nargs="+", default=None, help="profiling: override the problem extents")
+    parser.add_argument("--region-ms", type=float, default=1000.0,
+                        help="how long the timed trials of a workload last together (the clock sampler needs ~1 s)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -572,99 +790,48 @@ def main() -> int:
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the hot path")
     native.library()
     torch.cuda.set_device(local_rank)
-    distributed = world > 1
-    if distributed:
+    if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # the fused gather uses unicast peer stores only
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    warmup = max(args.warmup, 3)
-    workload = WORKLOADS[args.workload](torch, rank, world, args.size)
-    peaks, peak_kind = measured_peaks()
+    harness = Harness(torch, args, rank, world, local_rank)
+    extras = not args.kernel_only
+    headline_name = "gemm_bf16" if args.workload == "all" else args.workload
+    workload = WORKLOADS[headline_name](torch, rank, world, args.size)
+    head = harness.measure(workload, calls, native, e2e=extras, cpu=extras and not args.no_cpu_baseline, check=extras)
+    del workload
+    torch.cuda.empty_cache()
 
-    def barrier() -> None:
-        if distributed:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps: int) -> float:
-        """Milliseconds for `steps` calls of fn, on the device, max over ranks."""
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        barrier()
-        ms = torch.tensor([start.elapsed_time(stop)], device="cuda", dtype=torch.float64)
-        if distributed:
-            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
-        return float(ms.item())
-
-    # ---- resident-operand throughput ---------------------------------------------------------------------------------
-    for _ in range(warmup):
-        workload.step(calls)
-    with ClockSampler(local_rank) as sampler:
-        total_ms = timed(lambda: workload.step(calls), args.steps)
-        # keep the GPU busy long enough for nvidia-smi to see it under load; the kernel alone, because the number of
-        # iterations differs between ranks and a step of N > 1 holds a collective
-        deadline = time.time() + 0.6
-        while time.time() < deadline and len(sampler.samples) < 3:
-            workload.kernel_only(calls)
-            torch.cuda.synchronize()
-    clocks = sampler.summary()
-    native.raise_device_status()
-    ms_per_step = total_ms / args.steps
-    value = workload.scale(workload.work(), ms_per_step)
-
-    # ---- the dominant kernel alone (roofline) ---------------------------------------------------------------------
-    kernel_ms = timed(lambda: workload.kernel_only(calls), args.steps) / args.steps
-    achieved = workload.scale(workload.kernel_work(), kernel_ms)
-    peak, peak_note = workload.peak(peaks)
-    roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit, "frac": achieved / peak,
-                "traffic": None if args.size or world > 1 else NCU_TRAFFIC_BYTES[workload.name], "peak_kind": f"{peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
-    if workload.bound == "tensor":
-        nominal = 4500.0 if workload.dtype.startswith("fp8") else 2250.0
-        roofline["frac_of_nominal_dense_peak"] = achieved / nominal
-
-    # ---- end to end with host buffers ---------------------------------------------------------------------------------
-    e2e = None
-    e2e_error = None
-    if not args.kernel_only:
-        try:
-            h2d, d2h = workload.host_buffers()
-            for _ in range(2):
-                workload.e2e_step(calls)
-            e2e_steps = max(3, min(args.steps, 10))
-            e2e_ms = timed(lambda: workload.e2e_step(calls), e2e_steps) / e2e_steps
-            e2e = {"value": workload.scale(workload.work(), e2e_ms), "unit": workload.unit,
-                   "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms}
-            native.raise_device_status()
-        except Exception as error:  # the device-resident numbers above stand on their own; say why this leg is absent
-            e2e_error = f"{type(error).__name__}: {error}"
-
-    # ---- CPU baseline (rank 0, N = 1 only) ---------------------------------------------------------------------------
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.kernel_only:
-        from oracle import oracle
-
-        cores = min(os.cpu_count() or 1, 64)
-        work, sample, run = workload.cpu_sample(oracle, cores)
-        start = time.perf_counter()
-        run()
-        seconds = time.perf_counter() - start
-        cpu = {"value": workload.scale(work, seconds * 1e3), "unit": workload.unit, "cores": cores, "kind": "port",
-               "sample": sample, "seconds": seconds}
+    others = {}
+    if args.workload == "all" and not args.size:
+        for name in ("gemm_fp8", "attn_fwd", "attn_decode"):
+            try:
+                workload = WORKLOADS[name](torch, rank, world, None)
+                # with N > 1 the sub-records carry the device-resident numbers only (the run stays within minutes)
+                others[name] = harness.measure(workload, calls, native, e2e=extras and world == 1,
+                                               cpu=extras and world == 1 and not args.no_cpu_baseline,
+                                               check=extras and world == 1)
+                del workload
+            except Exception as error:  # one workload failing must not take the headline line with it
+                others[name] = {"error": f"{type(error).__name__}: {error}"}
+            torch.cuda.empty_cache()
 
     if rank == 0:
         line = {
-            "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic", "config": workload.config,
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": workload.launches_per_step * args.steps, "clocks": clocks,
+            "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
+            "config": head["config"], "roofline": head["roofline"], "cpu_baseline": head["cpu_baseline"],
+            "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": head["clocks"],
+            "timing": {"trials": head["trials"], "statistic": "median over trials of (ms of `steps` launches) / steps",
+                       "ms_per_step_min": head["ms_per_step_min"], "ms_per_step_max": head["ms_per_step_max"]},
         }
-        if e2e_error is not None:
-            line["e2e_error"] = e2e_error
+        for key in ("rel_frobenius", "e2e_error"):
+            if key in head:
+                line[key] = head[key]
+        if others:
+            line["workloads"] = others
         print(json.dumps(line), flush=True)
-    if distributed:
+    if world > 1:
         torch.distributed.destroy_process_group()
     return 0
 

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages; krn_b200_gemm_fp8 added */
+#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8 added */
 
 /* status codes */
 #define KRN_B200_OK 0
@@ -120,13 +120,21 @@ int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, const void*
  * c_of_rank[r] is the address, valid on this device, of rank r's full row-major C[M, ranks * n_local] (its own
  * buffer for r == rank, NVLink peer mappings for the others, e.g. from torch symmetric memory). The stores are TMA
  * stores issued tile by tile while the next tile is being multiplied; no load ever targets a peer and nothing is
- * multicast. A cross-rank barrier after the call (all ranks finished their kernel) makes every C complete.
+ * multicast. Every C is complete once all ranks' kernels have finished their stores: see sync_of_rank below.
  * n_local must be a multiple of 128 bytes of output (64 columns of bf16/f16, 32 of f32); all addresses and pitches
- * 16-byte aligned. `c_of_rank` is a HOST array of `ranks` pointers (ranks <= 8). No counterpart in the reference,
- * which has no multi-device path. */
+ * 16-byte aligned. `c_of_rank` is a HOST array of `ranks` pointers (ranks <= 8).
+ *   sync_of_rank  HOST array of `ranks` addresses (valid on this device) of each rank's 9 32-bit sync words — 8
+ *                 flags and an arrival counter, zero before the first product — or NULL. When given, the kernel's
+ *                 last CTA tells every peer that this rank's stores of product number `epoch` have landed and waits
+ *                 (at most about two seconds; on expiry the status word reports KRN_B200_ERR_DEVICE_TIMEOUT and the
+ *                 kernel returns) until every peer has said the same: when the kernel completes, this rank's C holds
+ *                 all column blocks and no separate barrier is needed. All ranks must then call with the same
+ *                 `epoch`, one more for every product (any start above zero). With NULL the caller runs its own
+ *                 cross-rank barrier after the call.
+ * No counterpart in the reference, which has no multi-device path. */
 int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank, int ranks,
                             int rank, int64_t m, int64_t n_local, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
-                            void* stream);
+                            void* const* sync_of_rank, uint32_t epoch, void* stream);
 
 /* C[M,N] = sum over 128-wide K blocks kb of  sa[m,kb] * sb[n/128,kb] * (A8[m, kb] . B8[n, kb]),
  * A8/B8 e4m3fn codes (one byte each, K-major), sa f32 [M, ceil(K/128)] (one scale per 1x128 block of A,
@@ -143,12 +151,13 @@ int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa,
  * epilogue, exactly as krn_b200_gemm_tn_gather does for the 16-bit product: rank `rank` multiplies A by ITS rows of B
  * (b: [n_local, K] codes, sb: [n_local / 128, ceil(K/128)] scales) and stores the column block
  * [rank * n_local, (rank + 1) * n_local) into every rank's C (c_of_rank: a HOST array of `ranks` addresses valid on
- * this device; TMA stores over NVLink, no peer loads, nothing multicast). n_local must be a multiple of 128. A
- * cross-rank barrier after the call makes every C complete. No counterpart in the reference. */
+ * this device; TMA stores over NVLink, no peer loads, nothing multicast). n_local must be a multiple of 128.
+ * sync_of_rank / epoch as in krn_b200_gemm_tn_gather (NULL: the caller runs a cross-rank barrier after the call).
+ * No counterpart in the reference. */
 int krn_b200_gemm_fp8_blockscaled_tn_gather(int c_type, const void* a, const float* sa, const void* b, const float* sb,
                                             void* const* c_of_rank, int ranks, int rank, int64_t m, int64_t n_local,
                                             int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
-                                            void* stream);
+                                            void* const* sync_of_rank, uint32_t epoch, void* stream);
 
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (batch, q head), the statement
  * sequence of the reference's example kernel (examples/04_libraries/08_flash_attention.py:44-59): scores

@@ -75,6 +75,7 @@ enum Site {
   kSitePromotionFull = 14,
   kSiteScaleEmpty = 15,
   kSitePromotionScale = 16,
+  kSiteRankBarrier = 17,
 };
 
 __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], int chunk, const uint32_t (&p)[32], float scale) {
@@ -89,7 +90,8 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], int chunk, const ui
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ Destinations dst, Problem p, Scales scales, DeviceStatus* status) {
+                const __grid_constant__ Destinations dst, Problem p, Scales scales,
+                const __grid_constant__ RankSync sync, DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
 
@@ -430,11 +432,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     tmem_dealloc<CTA_GROUP>(tmem_base, kTmemColumns);
   }
+  if (threadIdx.x == 0) rank_barrier_tail(sync, status, kSiteRankBarrier);
 }
 
 template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
-           Scales scales, cudaStream_t stream) {
+           Scales scales, const RankSync& sync, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_fp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
@@ -461,7 +464,7 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, scales, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, scales, sync, ctx->status_dev));
   return KRN_B200_OK;
 }
 
@@ -482,9 +485,12 @@ int fp8_pair_mode(int64_t m) { return m > kBM ? 2 : 1; }
 // for every destination d (each a row-major matrix of n_total columns with pitch ldc).
 static int fp8_product(int c_type, const void* a, const float* sa, const void* b, const float* sb,
                        void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m, int64_t n,
-                       int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle) {
+                       int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle,
+                       const krnb::RankSync* rank_sync = nullptr) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  RankSync sync = {};
+  if (rank_sync != nullptr) sync = *rank_sync;
   if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
     return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
   }
@@ -568,13 +574,13 @@ static int fp8_product(int c_type, const void* a, const float* sa, const void* b
                                    Swizzle::k128B)) return rc;
   }
   if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, scales, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, stream);
-    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, stream);
+    if (c_type == KRN_B200_F32) return launch<2, float, false>(ctx, map_a, map_b, dst, p, scales, sync, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, sync, stream);
+    return launch<2, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, sync, stream);
   }
-  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, stream);
-  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, stream);
+  if (c_type == KRN_B200_F32) return launch<1, float, false>(ctx, map_a, map_b, dst, p, scales, sync, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, uint16_t, true>(ctx, map_a, map_b, dst, p, scales, sync, stream);
+  return launch<1, uint16_t, false>(ctx, map_a, map_b, dst, p, scales, sync, stream);
 }
 
 extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b,
@@ -588,7 +594,8 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const
 extern "C" int krn_b200_gemm_fp8_blockscaled_tn_gather(int c_type, const void* a, const float* sa, const void* b,
                                                        const float* sb, void* const* c_of_rank, int ranks, int rank,
                                                        int64_t m, int64_t n_local, int64_t k, int64_t lda, int64_t ldb,
-                                                       int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle) {
+                                                       int64_t ldc, int64_t ldsa, int64_t ldsb,
+                                                       void* const* sync_of_rank, uint32_t epoch, void* stream_handle) {
   using namespace krnb;
   if (ranks < 1 || ranks > kMaxDestinations || rank < 0 || rank >= ranks || c_of_rank == nullptr) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "rank %d of %d: between 1 and %d ranks are supported", rank, ranks,
@@ -604,6 +611,8 @@ extern "C" int krn_b200_gemm_fp8_blockscaled_tn_gather(int c_type, const void* a
   }
   void* destinations[kMaxDestinations];
   for (int r = 0; r < ranks; ++r) destinations[r] = c_of_rank[r];
+  RankSync sync = {};
+  if (int rc = fill_rank_sync(&sync, sync_of_rank, ranks, rank, epoch)) return rc;
   return fp8_product(c_type, a, sa, b, sb, destinations, ranks, rank * n_local, n_local * ranks, m, n_local, k, lda, ldb,
-                     ldc, ldsa, ldsb, stream_handle);
+                     ldc, ldsa, ldsb, stream_handle, &sync);
 }

@@ -44,7 +44,7 @@ struct Layout {
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
 };
 
-enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4 };
+enum Site { kSiteProducerEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpilogueFull = 4, kSiteRankBarrier = 5 };
 
 // `values[i]` is this thread's accumulator for output column `col + i` (i < 32): add the bias of that column and apply
 // the activation, in f32, before the rounding. Lane l fetches the bias of column col + l once; the 32 columns are then
@@ -66,7 +66,7 @@ template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ Destinations dst, Problem p, EpilogueSpec epilogue, uint32_t a_format,
-               uint32_t b_format, DeviceStatus* status) {
+               uint32_t b_format, const __grid_constant__ RankSync sync, DeviceStatus* status) {
   using L = Layout<CTA_GROUP>;
   constexpr int kBK = kRowBytes / ELEM_BYTES;                 // K elements per stage
   // b as (K, N): the stage holds [kBK rows of K] x [128 bytes of N] blocks, one per kBlockCols output columns
@@ -338,11 +338,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     tmem_dealloc<CTA_GROUP>(tmem_base, kTmemColumns);
   }
+  if (threadIdx.x == 0) rank_barrier_tail(sync, status, kSiteRankBarrier);
 }
 
 template <int CTA_GROUP, int ELEM_BYTES, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const Destinations& mc, Problem p,
-           EpilogueSpec epilogue, uint32_t a_fmt, uint32_t b_fmt, cudaStream_t stream) {
+           EpilogueSpec epilogue, uint32_t a_fmt, uint32_t b_fmt, const RankSync& sync, cudaStream_t stream) {
   using L = Layout<CTA_GROUP>;
   auto kernel = gemm_tn_kernel<CTA_GROUP, ELEM_BYTES, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
@@ -361,22 +362,22 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, epilogue, a_fmt, b_fmt, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, ctx->status_dev));
   return KRN_B200_OK;
 }
 
 template <int ELEM_BYTES>
 int launch_for_output(const DeviceContext* ctx, int c_type, int group, const CUtensorMap& ma, const CUtensorMap& mb,
                       const Destinations& mc, Problem p, EpilogueSpec epilogue, uint32_t a_fmt, uint32_t b_fmt,
-                      cudaStream_t stream) {
+                      const RankSync& sync, cudaStream_t stream) {
   if (group == 2) {
-    if (c_type == KRN_B200_F32) return launch<2, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
-    if (c_type == KRN_B200_BF16) return launch<2, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
-    return launch<2, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+    if (c_type == KRN_B200_F32) return launch<2, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
+    if (c_type == KRN_B200_BF16) return launch<2, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
+    return launch<2, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
   }
-  if (c_type == KRN_B200_F32) return launch<1, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
-  if (c_type == KRN_B200_BF16) return launch<1, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
-  return launch<1, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, stream);
+  if (c_type == KRN_B200_F32) return launch<1, ELEM_BYTES, float, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
+  if (c_type == KRN_B200_BF16) return launch<1, ELEM_BYTES, uint16_t, true>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
+  return launch<1, ELEM_BYTES, uint16_t, false>(ctx, ma, mb, mc, p, epilogue, a_fmt, b_fmt, sync, stream);
 }
 
 // Operands whose addresses or row pitches are not multiples of 16 bytes cannot be described to TMA. They take this
@@ -467,10 +468,13 @@ static bool is_16bit(int type) { return type == KRN_B200_BF16 || type == KRN_B20
 static int tiled_product(const krnb::DeviceContext* ctx, int a_type, int b_type, int c_type, const void* a, const void* b,
                          void* const* destinations, int count, int64_t column_offset, int64_t n_total, int64_t m,
                          int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int group, cudaStream_t stream,
-                         bool b_kn = false, krnb::EpilogueSpec epilogue = {nullptr, 0}) {
+                         bool b_kn = false, krnb::EpilogueSpec epilogue = {nullptr, 0},
+                         const krnb::RankSync* rank_sync = nullptr) {
   using namespace krnb;
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
   const bool fp8 = is_fp8(a_type);
+  RankSync sync = {};
+  if (rank_sync != nullptr) sync = *rank_sync;
   const int ab_bytes = fp8 ? 1 : 2;
   const uint32_t row_elements = uint32_t(128 / ab_bytes);  // elements in one 128-byte swizzle row
   Problem p;
@@ -521,10 +525,10 @@ static int tiled_product(const krnb::DeviceContext* ctx, int a_type, int b_type,
   if (fp8) {
     const uint32_t a_fmt = a_type == KRN_B200_E4M3 ? kFmtE4M3 : kFmtE5M2;
     const uint32_t b_fmt = b_type == KRN_B200_E4M3 ? kFmtE4M3 : kFmtE5M2;
-    return launch_for_output<1>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, a_fmt, b_fmt, stream);
+    return launch_for_output<1>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, a_fmt, b_fmt, sync, stream);
   }
   const uint32_t fmt = a_type == KRN_B200_BF16 ? kFmtBF16 : kFmtF16;
-  return launch_for_output<2>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, fmt, fmt, stream);
+  return launch_for_output<2>(ctx, c_type, group, map_a, map_b, dst, p, epilogue, fmt, fmt, sync, stream);
 }
 
 // Argument checks, the K == 0 and unaligned cases and the launch, shared by the two layouts of b and by the 16-bit and
@@ -641,7 +645,8 @@ extern "C" int krn_b200_matmul(int ab_type, int c_type, int b_kn, int epilogue, 
 
 extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* b, void* const* c_of_rank,
                                        int ranks, int rank, int64_t m, int64_t n_local, int64_t k, int64_t lda,
-                                       int64_t ldb, int64_t ldc, void* stream_handle) {
+                                       int64_t ldb, int64_t ldc, void* const* sync_of_rank, uint32_t epoch,
+                                       void* stream_handle) {
   using namespace krnb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (ab_type != KRN_B200_BF16 && ab_type != KRN_B200_F16) {
@@ -677,9 +682,11 @@ extern "C" int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, c
   if (!aligned) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the sharded product needs 16-byte aligned addresses and row pitches");
   }
+  RankSync sync = {};
+  if (int rc = fill_rank_sync(&sync, sync_of_rank, ranks, rank, epoch)) return rc;
   DeviceContext* ctx = current_context();
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
   return tiled_product(ctx, ab_type, ab_type, c_type, a, b, destinations, ranks, rank * n_local, n_local * ranks, m,
-                       n_local, k, lda, ldb, ldc, gemm_pair_mode(m), stream);
+                       n_local, k, lda, ldb, ldc, gemm_pair_mode(m), stream, false, EpilogueSpec{nullptr, 0}, &sync);
 }

@@ -5,6 +5,7 @@ missing kernel library raises `LibraryNotFound`."""
 from __future__ import annotations
 
 import ctypes
+import sys
 from typing import Any
 
 from krn_b200.runtime import native
@@ -35,7 +36,12 @@ def _pitch(tensor: Any) -> int:
 
 
 def _stream(stream: Any) -> ctypes.c_void_p:
+    """The CUDA stream handle to enqueue on. None means torch's CURRENT stream when torch is loaded (so a call made
+    under `with torch.cuda.stream(s)` lands on s like torch's own work), else the legacy default stream."""
     if stream is None:
+        torch = sys.modules.get("torch")
+        if torch is not None and torch.cuda.is_available():
+            return ctypes.c_void_p(int(torch.cuda.current_stream().cuda_stream))
         return ctypes.c_void_p(0)
     if hasattr(stream, "cuda_stream"):
         return ctypes.c_void_p(int(stream.cuda_stream))
@@ -102,10 +108,20 @@ def matmul(a: Any, b: Any, c: Any, *, b_kn: bool = True, epilogue: int = 0, bias
     native.check(status, "tile matrix product with epilogue")
 
 
+def _sync_array(sync_pointers: list[int] | None, ranks: int):
+    if sync_pointers is None:
+        return None
+    if len(sync_pointers) != ranks:
+        raise ValueError(f"{len(sync_pointers)} sync addresses for {ranks} ranks")
+    return (ctypes.c_void_p * ranks)(*sync_pointers)
+
+
 def gemm_tn_gather(a: Any, b_local: Any, c_pointers: list[int], rank: int, m: int, n_local: int, ldc: int, c_type: int,
-                   stream: Any = None) -> None:
+                   stream: Any = None, sync_pointers: list[int] | None = None, epoch: int = 0) -> None:
     """This rank's column block of c = a @ b^T, stored by the kernel's epilogue into every rank's full C.
-    `c_pointers[r]` is the address (valid on this device) of rank r's row-major C[m, len(c_pointers) * n_local]."""
+    `c_pointers[r]` is the address (valid on this device) of rank r's row-major C[m, len(c_pointers) * n_local].
+    `sync_pointers[r]` (optional) is the address of rank r's 9 sync words: with them the kernel itself waits until every
+    rank's stores of product number `epoch` have landed; without them the caller runs a cross-rank barrier."""
     (rows, k), (nb, kb) = a.shape, b_local.shape
     if kb != k or rows != m or nb != n_local:
         raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b_local.shape)}, block {m} x {n_local}")
@@ -113,7 +129,7 @@ def gemm_tn_gather(a: Any, b_local: Any, c_pointers: list[int], rank: int, m: in
     array = (ctypes.c_void_p * ranks)(*c_pointers)
     status = native.library().krn_b200_gemm_tn_gather(
         _type_of(a), c_type, _pointer(a), _pointer(b_local), array, ranks, rank, m, n_local, k, _pitch(a), _pitch(b_local),
-        ldc, _stream(stream))
+        ldc, _sync_array(sync_pointers, ranks), epoch & 0xFFFFFFFF, _stream(stream))
     native.check(status, "column-sharded tile matrix product")
 
 
@@ -132,7 +148,8 @@ def gemm_fp8_blockscaled_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: An
 
 
 def gemm_fp8_blockscaled_tn_gather(a: Any, sa: Any, b_local: Any, sb_local: Any, c_pointers: list[int], rank: int,
-                                   n_local: int, ldc: int, c_type: int, stream: Any = None) -> None:
+                                   n_local: int, ldc: int, c_type: int, stream: Any = None,
+                                   sync_pointers: list[int] | None = None, epoch: int = 0) -> None:
     """This rank's column block of the block-scaled FP8 product, stored by the kernel's epilogue into every rank's
     full C (`c_pointers[r]` = address on this device of rank r's row-major C[m, len(c_pointers) * n_local])."""
     (m, k), (nb, kb) = a.shape, b_local.shape
@@ -144,7 +161,8 @@ def gemm_fp8_blockscaled_tn_gather(a: Any, sa: Any, b_local: Any, sb_local: Any,
     array = (ctypes.c_void_p * ranks)(*c_pointers)
     status = native.library().krn_b200_gemm_fp8_blockscaled_tn_gather(
         c_type, _pointer(a), _pointer(sa), _pointer(b_local), _pointer(sb_local), array, ranks, rank, m, n_local, k,
-        _pitch(a), _pitch(b_local), ldc, _pitch(sa), _pitch(sb_local), _stream(stream))
+        _pitch(a), _pitch(b_local), ldc, _pitch(sa), _pitch(sb_local), _sync_array(sync_pointers, ranks),
+        epoch & 0xFFFFFFFF, _stream(stream))
     native.check(status, "column-sharded block-scaled FP8 tile matrix product")
 
 

@@ -30,12 +30,12 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
     "krn_b200_matmul": (_int, [_int, _int, _int, _int, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_nn": (_int, [_int, _int, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_tn_gather": (_int, [_int, _int, _ptr, _ptr, ctypes.POINTER(_ptr), _int, _int, _i64, _i64, _i64, _i64,
-                                       _i64, _i64, _ptr]),
+                                       _i64, _i64, ctypes.POINTER(_ptr), ctypes.c_uint32, _ptr]),
     "krn_b200_gemm_fp8_blockscaled_tn": (
         _int, [_int, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_fp8_blockscaled_tn_gather": (
         _int, [_int, _ptr, _ptr, _ptr, _ptr, ctypes.POINTER(_ptr), _int, _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
-               _i64, _ptr]),
+               _i64, ctypes.POINTER(_ptr), ctypes.c_uint32, _ptr]),
     "krn_b200_attn_fwd": (
         _int, [_int, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int,
                ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _ptr]),

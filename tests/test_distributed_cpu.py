@@ -82,3 +82,14 @@ def test_sharding_tables() -> None:
     loads = [int(lengths[t].sum()) for t in table]
     assert max(loads) - min(loads) <= int(lengths.max())  # the LPT bound
     assert max(loads) <= 1.05 * sum(loads) / 8
+
+
+def test_gather_schedule_alternates_copies_and_numbers_products() -> None:
+    """Product i writes copy (i - 1) % buffers and carries number i: the bookkeeping that keeps a peer's stores out of a
+    copy of C that is still being read."""
+    schedule = sharding.GatherSchedule(2)
+    assert [schedule.next() for _ in range(5)] == [(0, 1), (1, 2), (0, 3), (1, 4), (0, 5)]
+    single = sharding.GatherSchedule(1)
+    assert [single.next() for _ in range(3)] == [(0, 1), (0, 2), (0, 3)]
+    with pytest.raises(ValueError):
+        sharding.GatherSchedule(0)

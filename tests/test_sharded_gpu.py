@@ -23,7 +23,8 @@ def _rank(rank: int, world: int, port: int, failures) -> None:
     import torch
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -39,13 +40,26 @@ def _rank(rank: int, world: int, port: int, failures) -> None:
         calls.gemm_tn(a, b, whole)
         begin, end = sharding.column_block(n, rank, world, 64)
 
+        from krn_b200.runtime import native
+
         fused = sharding.GatheredProduct(m, n, torch.bfloat16)
-        fused.c.fill_(float("nan"))
-        dist.barrier()
-        result = fused.run(a, b[begin:end])
+        for c in fused.copies:
+            c.fill_(float("nan"))
         torch.cuda.synchronize()
-        if not torch.equal(result, whole):
-            failures.put(f"rank {rank}: the fused gather does not hold the whole product")
+        dist.barrier()
+        # three products in a row on a side stream, each read back (on that stream) before the next is enqueued: the
+        # kernel's own tail is the only cross-rank synchronisation
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        sums = []
+        with torch.cuda.stream(side):
+            for scale in (1, 2, 3):
+                result = fused.run(a * scale, b[begin:end])
+                sums.append((result.float() - whole.float() * scale).abs().max())
+        side.synchronize()
+        native.raise_device_status()
+        if any(float(x) != 0.0 for x in sums):
+            failures.put(f"rank {rank}: the fused gather does not hold the whole product: {[float(x) for x in sums]}")
 
         streamed = streaming.ShardedStreamedProduct(m, end - begin, k, torch.bfloat16, panels=2)
         c_host = torch.full((m, end - begin), float("nan"), dtype=torch.bfloat16).pin_memory()
