@@ -484,7 +484,7 @@ class AttnDecode(Workload):
     unit, bound = "GB/s", "hbm"
     description = "FP8 e4m3 paged decode attention B=64 Hq=32 Hkv=8 D=128, contexts U[1024,8192], page 64 (seed 4)"
     batch, hq, hkv, d, page = 64, 32, 8, 128, 64
-    launches_per_step = 1  # one kernel (a memset node of the counters precedes it)
+    launches_per_step = 2  # the split-KV kernel and its merge
 
     def __init__(self, torch, rank, world, size=None) -> None:
         super().__init__(torch, rank, world)
@@ -511,8 +511,9 @@ class AttnDecode(Workload):
             cursor += int(count)
         gen = torch.Generator(device="cuda").manual_seed(4 + rank)
         shape = (pool, self.page, self.hkv, self.d)
-        self.k_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).to(torch.float8_e4m3fn)
-        self.v_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).to(torch.float8_e4m3fn)
+        # codes of N(0, 1) * 100 clamped into the finite e4m3 range (the conversion itself does not saturate)
+        self.k_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        self.v_pages = (torch.randn(shape, device="cuda", generator=gen) * 100).clamp_(-448, 448).to(torch.float8_e4m3fn)
         self.k_scale = torch.rand((self.local, self.hkv), device="cuda", generator=gen) * 0.01 + 0.005
         self.v_scale = torch.rand((self.local, self.hkv), device="cuda", generator=gen) * 0.01 + 0.005
         self.q = torch.randn((self.local, self.hq, self.d), device="cuda", generator=gen).to(torch.bfloat16)

@@ -173,8 +173,7 @@ int krn_b200_attn_fwd(int type, const void* q, const void* k, const void* v, voi
                       const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                       const int64_t* o_strides, void* stream);
 
-/* Bytes of caller workspace krn_b200_attn_decode_fp8_paged needs for these extents (split-KV partials and the
- * kernel's counters). */
+/* Bytes of caller workspace krn_b200_attn_decode_fp8_paged needs for these extents (split-KV partials). */
 int64_t krn_b200_attn_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t d, int64_t max_context);
 
 /* Decode attention (one query token per sequence) over a paged e4m3 KV cache. The reference has no
@@ -182,15 +181,14 @@ int64_t krn_b200_attn_decode_workspace_bytes(int64_t batch, int64_t q_heads, int
  * statements above with K and V dequantised as code * scale.
  *   q  bf16 [batch, q_heads, d]         o  bf16 [batch, q_heads, d]
  *   k_pages, v_pages  e4m3 codes [num_pages, page_size, kv_heads, d]
- *   num_pages   pages in the pool. It bounds every fetch: a page id outside [0, num_pages) is never read — its
- *               keys count as absent and KRN_B200_ERR_DEVICE_INDEX is left in the status word.
+ *   num_pages   pages in the pool. It bounds every fetch: a page id outside [0, num_pages) is never read — its 64
+ *               tokens read as zero codes (K = V = 0) and KRN_B200_ERR_DEVICE_INDEX is left in the status word.
  *   page_table  int32 [batch, max_pages_per_seq]: page ids of each sequence in order; entries past a sequence's
  *               context are never looked at
  *   context_len int32 [batch]; values are clamped into [0, max_context]; a sequence of length 0 gets zeros
  *   k_scale, v_scale  f32 [batch, kv_heads]
  *   workspace   at least krn_b200_attn_decode_workspace_bytes(...) bytes, 16-byte aligned; contents need no
- *               preparation (the call clears the counters it keeps there with a memset on `stream`)
- * One kernel: the chunk of a (sequence, kv head) that finishes last combines the split-KV partials. */
+ *               preparation (a call reads back only the partials it wrote) */
 int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
                                    const int32_t* context_len, const float* k_scale, const float* v_scale, void* o,
                                    int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t d, int64_t page_size,
@@ -200,17 +198,15 @@ int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages, const voi
 /* The same computation as krn_b200_attn_decode_fp8_paged, for callers that cannot allocate device memory when
  * they need it — a serving loop whose KV-cache pool owns all remaining HBM, a plugin confined to another
  * runtime's memory budget, a path where cudaMalloc's implicit synchronisation is not allowed. The split-KV
- * partials and the kernel's counters go to a 16 MiB array built into the library image (each GPU that loads the
- * library holds it until the process exits) instead of a caller workspace; the entry point calls no allocating
- * routine at all.
- *   limit    batch * q_heads * (ceil(max_context / 1024) * 130 + 1) + 1 words must fit 16 MiB (4 Mi words); larger
+ * partials go to a 16 MiB array built into the library image (each GPU that loads the library holds it until the
+ * process exits) instead of a caller workspace; the entry point calls no allocating routine at all.
+ *   limit    batch * q_heads * ceil(max_context / 1024) * 130 floats must fit 16 MiB (4 Mi floats); larger
  *            problems are refused with KRN_B200_ERR_WORKSPACE — use the workspace variant for those.
  *   set-up   the first call on each device resolves the array's device address (cudaGetSymbolAddress); make
  *            that first call outside any stream capture.
- *   sharing  every call on a device uses the same array, which keeps the previous call's contents. The only part
- *            that must start at zero, the counters, is cleared by a memset the call enqueues on `stream` before the
- *            kernel; the partials are read back only where this call wrote them. Two calls whose kernels overlap
- *            on the GPU — different streams, or a graph replayed concurrently — race on the array: serialise them.
+ *   sharing  every call on a device uses the same array, which keeps the previous call's partials. Nothing in
+ *            it has to start at zero (a call reads back only what it wrote), but two calls whose kernels overlap
+ *            on the GPU — different streams, or a graph replayed concurrently — race on it: serialise them.
  *   status   a bounded device-side wait that expires (or an out-of-range page id) is recorded in the status word
  *            only if an earlier call of another entry point created that word on this device; this entry point
  *            does not create it.

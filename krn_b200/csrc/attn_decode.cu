@@ -1,7 +1,7 @@
 // Decode attention (one query token per sequence) over a paged FP8 e4m3 KV cache, split over the keys.
 //
-// Work unit = (sequence b, kv head g, 1024-token chunk of the context). The four q heads that share kv head g are
-// handled together, so every K/V byte is read from HBM once. The path is HBM-bound (about 8 flop per byte); the tensor
+// Work unit = (sequence b, kv head g, chunk of the context). The four q heads that share kv head g are handled
+// together, so every K/V byte is read from HBM once. The path is HBM-bound (about 8 flop per byte); the tensor
 // cores are used only to keep the arithmetic off the critical path, with the cache bytes consumed exactly as
 // they sit in memory:
 //
@@ -16,14 +16,17 @@
 //     MMA 2    D[d, col] = V_tile^T . P8^T           M = d = 128, N = 16, K = 128 tokens; V is an MN-major
 //              operand (d contiguous), i.e. the cache layout itself
 //     threads  one thread per OUTPUT COLUMN d: acc[h] = acc[h] * corr[h] + (D[d,h] + D[d,4+h]) * 2^-8
-//   end      partial (m, l, acc) per (b, q head, chunk) to the scratch area; the CTA that finishes the LAST chunk of a
-//            (sequence, kv head) combines the chunks, applies v_scale and rounds once to bf16 (an arrival counter per
-//            (b, g) decides who is last: no second kernel, no spin).
+//   end      partial (m, l, acc) per (b, q head, chunk) to the workspace; a second kernel, launched as a programmatic
+//            dependent so that its launch overlaps this kernel's tail, merges the chunks, applies v_scale and rounds
+//            once to bf16.
 //
-// One launch of at most 3 CTAs per SM runs all units: a scheduler warp per CTA claims unit numbers from a global
-// ticket counter one unit ahead of the four compute warps, skipping the chunks that lie beyond a sequence's context,
-// so CTAs never idle while work remains and the end of the launch is made of the short last chunks. Units are
-// numbered chunk-major (chunk 0 of every sequence first), which puts the sparse, short high chunks last.
+// Measured alternatives on the benchmark mix (64 sequences, contexts 1024..8192; this layout: 126 us per call):
+//   * merging inside this kernel (an arrival counter per (sequence, kv head); the CTA that finishes the last chunk
+//     merges): the fence, the atomic and the merge sit on every CTA's critical path, +36 us;
+//   * one persistent launch of 3 CTAs per SM taking work units from a ticket counter, with a table of the units that
+//     exist so that no CTA is spent on a chunk beyond a context: 141 us — relaunching a CTA per unit costs less than
+//     the per-unit bookkeeping, and the hardware scheduler already keeps every slot busy;
+//   * a bounds report or a shared-memory flag inside the loop of the thread that issues the copies: +31 / +15 us.
 //
 // The reference has no implementation of paged decode attention (its roadmap lists it); the arithmetic follows
 // its flash-attention statements (examples/04_libraries/08_flash_attention.py:44-59) with K, V = code * scale.
@@ -42,27 +45,24 @@ constexpr int kPage = 64;
 constexpr int kIterTokens = 128;       // two pages
 constexpr int kChunkTokens = 1024;     // tokens per work unit (8 iterations)
 constexpr int kGroupMax = 4;           // q heads per kv head handled by one CTA
-constexpr int kComputeThreads = 128;   // warps 0..3: one thread per token / per output column
-constexpr int kThreads = 160;          // + warp 4: the scheduler
+constexpr int kThreads = 128;
 constexpr int kStages = 2;
 constexpr int kTileBytes = kIterTokens * 128;  // 16 KB: 128 tokens x 128 B
 constexpr int kSmemBytes = kStages * 2 * kTileBytes + 2048 /*Q8*/ + 2048 /*P8*/ + 1024 /*misc*/ + 1024 /*align*/;
-constexpr int kErrDeviceIndex = 6;     // mirrors KRN_B200_ERR_DEVICE_INDEX in include/krn_b200.h
 
 struct DecodeParams {
   const uint16_t* q;          // bf16 [batch, q_heads, d]
   const int32_t* page_table;  // [batch, max_pages]
   const int32_t* context_len; // [batch]
   const float* k_scale;       // [batch, kv_heads]
-  const float* v_scale;       // [batch, kv_heads]
-  uint16_t* o;                // bf16 [batch, q_heads, d]
-  float* partials;            // [batch, q_heads, chunks, d + 2]
-  int* counters;              // [0] unit tickets, [1 + b * kv_heads + g] arrivals of finished chunks; zero at launch
-  int batch, q_heads, kv_heads, group, max_pages, chunks, max_context, num_pages;
+  float* workspace;           // partials
+  int batch, q_heads, kv_heads, group, max_pages, chunks, num_pages, max_context;
   float scale_log2;
 };
 
-enum Site { kSiteKv = 31, kSiteMma1 = 32, kSiteMma2 = 33, kSiteUnitFull = 34, kSiteUnitEmpty = 35, kSitePageId = 36 };
+constexpr int kErrDeviceIndex = 6;  // mirrors KRN_B200_ERR_DEVICE_INDEX in include/krn_b200.h
+
+enum Site { kSiteKv = 31, kSiteMma1 = 32, kSiteMma2 = 33, kSitePageId = 36 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t w) { return __uint_as_float(uint32_t(w) << 16); }
 
@@ -110,19 +110,19 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
   return __all_sync(0xffffffffu, ok);
 }
 
-
-// Barrier over the four compute warps only (the scheduler warp never joins it).
-__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory"); }
-
-// Tokens of sequence b that count: the context length clamped into [0, max_context], so a length beyond what the page
-// table row holds can never index past the row.
-__device__ __forceinline__ int clamped_len(const DecodeParams& p, int b) {
-  return max(0, min(p.context_len[b], p.max_context));
-}
-
 __global__ void __launch_bounds__(kThreads, 3)
-decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeParams p,
-              DeviceStatus* status) {
+decode_partial_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      DecodeParams p, DeviceStatus* status) {
+  const int chunk = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  // the context length is clamped into [0, max_context]: a length beyond what the page table row holds can never
+  // index past the row
+  const int len = max(0, min(p.context_len[b], p.max_context));
+  const int token0 = chunk * kChunkTokens;
+  if (token0 >= len) return;  // whole CTA leaves together, before any barrier or allocation
+  int bad_page = 0;  // thread 0: bit 31 set once a page id outside the pool was met (low bits: part of the id)
+  const int tokens = min(kChunkTokens, len - token0);
+  const int iters = (tokens + kIterTokens - 1) / kIterTokens;
+
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -134,28 +134,17 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   uint8_t* misc = smem + 2 * kStages * kTileBytes + 4096;
   const uint32_t kv_full = smem_u32(misc);                   // [kStages]
   const uint32_t mma_bar = kv_full + 8 * kStages;            // one barrier, alternating phases
-  const uint32_t unit_full = mma_bar + 8;                    // [2] scheduler -> compute: a unit number is posted
-  const uint32_t unit_empty = unit_full + 16;                // [2] compute -> scheduler: the slot was read
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 64);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 68);
-  volatile int* unit_slot = reinterpret_cast<volatile int*>(misc + 72);   // [2]
-  volatile int* bad_pages = reinterpret_cast<volatile int*>(misc + 80);   // [kStages] bit pg: page pg of the stage is out of range
-  volatile int* last_flag = reinterpret_cast<volatile int*>(misc + 96);
-  float* red = reinterpret_cast<float*>(misc + 128);         // [4 warps][4 heads] scratch
+  float* red = reinterpret_cast<float*>(misc + 128);         // [4 warps][4 heads] scratch, then reuse
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const uint32_t lane = lane_id();
   const int group = p.group;  // q heads per kv head (<= 4)
-  const int bg_count = p.batch * p.kv_heads;
-  const int total_units = p.chunks * bg_count;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(kv_full + 8 * s, 1);
     mbar_init(mma_bar, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(unit_full + 8 * s, 1);
-      mbar_init(unit_empty + 8 * s, 1);
-    }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_k);
@@ -165,7 +154,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     tmem_alloc<1>(smem_u32(tmem_slot), 32);
     tmem_relinquish<1>();
   }
-  // zero the Q8 and P8 operand tiles once (rows 8..15 are never written and must read as zero codes)
+  // zero the Q8 and P8 operand tiles (rows that stay unused must read as zero codes)
   for (int i = tid; i < 4096 / 16; i += kThreads) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(q8_tile + i * 16), "r"(0u) : "memory");
   }
@@ -174,294 +163,208 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
-    // ---------------------------------------------------------------- scheduler: one unit ahead of the compute warps
-    if (lane == 0) {
-      for (uint32_t n = 0;; ++n) {
-        const uint32_t slot = n & 1u;
-        if (!mbar_wait(unit_empty + 8 * slot, ((n >> 1) & 1u) ^ 1u, abort_flag, status, kSiteUnitEmpty)) break;
-        int u;
-        while (true) {
-          u = atomicAdd(p.counters, 1);
-          if (u >= total_units) break;
-          const int chunk = u / bg_count;
-          const int b = (u - chunk * bg_count) / p.kv_heads;
-          // chunk 0 always runs (a sequence without tokens still has its output rows to write)
-          if (chunk == 0 || chunk * kChunkTokens < clamped_len(p, b)) break;
-        }
-        unit_slot[slot] = u < total_units ? u : -1;
-        mbar_arrive(unit_full + 8 * slot);  // release: the slot write is visible to whoever sees the phase flip
-        if (u >= total_units) break;
+  // ---- TMA issue for one iteration (thread 0): two pages of K and two of V into stage `stage`
+  const int32_t* pages = p.page_table + (long long)b * p.max_pages + token0 / kPage;
+  auto issue_loads = [&](int it) {
+    const int stage = it % kStages;
+    const int first = it * 2;
+    const int valid_pages = min(2, (tokens - it * kIterTokens + kPage - 1) / kPage);
+    mbar_arrive_expect_tx(kv_full + 8 * stage, uint32_t(valid_pages) * 2u * kPage * 128u);
+    for (int pg = 0; pg < valid_pages; ++pg) {
+      int page = pages[first + pg];
+      // A page id outside the pool is never fetched: the copy is aimed one past the pool, where the tensor map's bounds
+      // make TMA fill zeros, so those 64 tokens read as zero codes (K = V = 0). Only a compare and a select sit here —
+      // this thread's loop is the kernel's critical path (a status report at this point cost 31 us per call, a
+      // shared-memory flag read by the softmax threads another 15); the report is made once, at the end.
+      if (uint32_t(page) >= uint32_t(p.num_pages)) {
+        bad_page = page | int(0x80000000);
+        page = p.num_pages;
       }
+      tma_load_4d(k_tiles + stage * kTileBytes + pg * kPage * 128, &map_k, 0, g, 0, page, kv_full + 8 * stage);
+      tma_load_4d(v_tiles + stage * kTileBytes + pg * kPage * 128, &map_v, 0, g, 0, page, kv_full + 8 * stage);
     }
-  } else {
-    // ---------------------------------------------------------------- compute warps
-    const uint32_t idesc1 = umma_idesc(kFmtE4M3, kFmtE4M3, 128, 16, 0, 0);
-    const uint32_t idesc2 = umma_idesc(kFmtE4M3, kFmtE4M3, 128, 16, 1, 0);
-    const uint32_t lane_base = tmem_base + (uint32_t(warp * 32) << 16);
-    uint32_t mma_phase = 0;
-    uint32_t loads = 0;  // K/V stage fills so far in this CTA: stage = loads % kStages, parity = (loads / kStages) & 1
-    bool ok = true;
+  };
+  if (tid == 0) {
+    for (int it = 0; it < min(iters, kStages); ++it) issue_loads(it);
+  }
 
-    for (uint32_t n = 0; ok; ++n) {
-      const uint32_t slot = n & 1u;
-      if (!warp_wait(unit_full + 8 * slot, (n >> 1) & 1u, abort_flag, status, kSiteUnitFull)) break;
-      const int unit = unit_slot[slot];
-      compute_sync();  // every compute thread holds the unit number: the slot may be refilled
-      if (tid == 0) mbar_arrive(unit_empty + 8 * slot);
-      if (unit < 0) break;
-
-      const int chunk = unit / bg_count;
-      const int bg = unit - chunk * bg_count;
-      const int b = bg / p.kv_heads, g = bg - b * p.kv_heads;
-      const int len = clamped_len(p, b);
-      const int token0 = chunk * kChunkTokens;
-      if (len == 0) {
-        // nothing to attend to: the output rows are zeros (only chunk 0 of such a sequence is ever scheduled)
-        for (int h = 0; h < group; ++h) p.o[((long long)b * p.q_heads + g * group + h) * kD + tid] = 0;
-        continue;
+  // ---- Q8 operand: per head, q * 2^e with 2^e chosen so the largest magnitude lands below 448, as hi + lo codes
+  // thread `tid` owns column d = tid
+  float q_inv_scale[kGroupMax];  // 2^-e per head (folded into the score scale)
+  {
+    float qv[kGroupMax];
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) {
+      qv[h] = h < group ? bf16_bits_to_float(p.q[((long long)b * p.q_heads + g * group + h) * kD + tid]) : 0.f;
+      float a = fabsf(qv[h]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+      if (lane == 0) red[warp * 4 + h] = a;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) {
+      const float amax = fmaxf(fmaxf(red[h], red[4 + h]), fmaxf(red[8 + h], red[12 + h]));
+      // power of two: exact to apply and to undo; 256 * amax' <= 448 keeps both codes in range
+      int e = 0;
+      if (amax > 0.f) {
+        frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
+        e = 8 - e;         // q * 2^(8-e) has magnitude in [128, 256)
       }
-      const int tokens = min(kChunkTokens, len - token0);
-      const int iters = (tokens + kIterTokens - 1) / kIterTokens;
-      const uint32_t first_load = loads;
+      const float up = ldexpf(1.0f, e);
+      q_inv_scale[h] = ldexpf(1.0f, -e);
+      const float scaled = qv[h] * up;
+      const uint32_t hi = to_e4m3(scaled);
+      const uint32_t lo = to_e4m3(scaled - from_e4m3(hi));
+      st_shared_u8(swizzled(q8_tile, h, tid), hi);
+      st_shared_u8(swizzled(q8_tile, 4 + h, tid), lo);
+    }
+    __syncthreads();  // red[] is reused below
+  }
+  float score_scale[kGroupMax];
+  {
+    const float ks = p.k_scale[b * p.kv_heads + g] * p.scale_log2;
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) score_scale[h] = q_inv_scale[h] * ks;
+  }
+  fence_async_smem();
+  __syncthreads();
 
-      // ---- TMA issue for one iteration (thread 0): two pages of K and two of V into the iteration's stage
-      const int32_t* pages = p.page_table + (long long)b * p.max_pages + token0 / kPage;
-      auto issue_loads = [&](int it) {
-        const uint32_t stage = (first_load + uint32_t(it)) % kStages;
-        const int first = it * 2;
-        const int valid_pages = min(2, (tokens - it * kIterTokens + kPage - 1) / kPage);
-        mbar_arrive_expect_tx(kv_full + 8 * stage, uint32_t(valid_pages) * 2u * kPage * 128u);
-        int bad = 0;
-        for (int pg = 0; pg < valid_pages; ++pg) {
-          int page = pages[first + pg];
-          if (uint32_t(page) >= uint32_t(p.num_pages)) {
-            // a page id outside the pool: its keys count as absent. The copy still runs, aimed one past the pool,
-            // where the tensor map's bounds make TMA fill zeros instead of reading memory.
-            bad |= 1 << pg;
-            report_failure(status, kErrDeviceIndex, kSitePageId, uint32_t(page));
-            page = p.num_pages;
-          }
-          tma_load_4d(k_tiles + stage * kTileBytes + pg * kPage * 128, &map_k, 0, g, 0, page, kv_full + 8 * stage);
-          tma_load_4d(v_tiles + stage * kTileBytes + pg * kPage * 128, &map_v, 0, g, 0, page, kv_full + 8 * stage);
-        }
-        bad_pages[stage] = bad;
-      };
-      if (tid == 0) {
-        for (int it = 0; it < min(iters, kStages); ++it) issue_loads(it);
-      }
+  const uint32_t idesc1 = umma_idesc(kFmtE4M3, kFmtE4M3, 128, 16, 0, 0);
+  const uint32_t idesc2 = umma_idesc(kFmtE4M3, kFmtE4M3, 128, 16, 1, 0);
+  const uint32_t lane_base = tmem_base + (uint32_t(warp * 32) << 16);
+  float m_run[kGroupMax], l_part[kGroupMax], acc[kGroupMax];
+#pragma unroll
+  for (int h = 0; h < kGroupMax; ++h) {
+    m_run[h] = -INFINITY;
+    l_part[h] = 0.f;
+    acc[h] = 0.f;
+  }
+  uint32_t mma_phase = 0;
+  bool ok = true;
 
-      // ---- Q8 operand: per head, q * 2^e with 2^e chosen so the largest magnitude lands below 448, as hi + lo codes
-      // thread `tid` owns column d = tid
-      float q_inv_scale[kGroupMax];  // 2^-e per head (folded into the score scale)
-      {
-        float qv[kGroupMax];
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) {
-          qv[h] = h < group ? bf16_bits_to_float(p.q[((long long)b * p.q_heads + g * group + h) * kD + tid]) : 0.f;
-          float a = fabsf(qv[h]);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-          if (lane == 0) red[warp * 4 + h] = a;
+  for (int it = 0; it < iters && ok; ++it) {
+    const int stage = it % kStages;
+    const uint32_t k_tile = k_tiles + stage * kTileBytes;
+    const uint32_t v_tile = v_tiles + stage * kTileBytes;
+    const int valid = min(kIterTokens, tokens - it * kIterTokens);
+    if (!warp_wait(kv_full + 8 * stage, (it / kStages) & 1, abort_flag, status, kSiteKv)) {
+      ok = false;
+      break;
+    }
+    if (valid < kIterTokens) {
+      // rows past the context end hold stale or unloaded bytes: make them zero codes so 0 * x stays 0
+      if (tid >= valid) {
+        for (int c = 0; c < 8; ++c) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_tile + tid * 128 + c * 16), "r"(0u) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + tid * 128 + c * 16), "r"(0u) : "memory");
         }
-        compute_sync();
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) {
-          const float amax = fmaxf(fmaxf(red[h], red[4 + h]), fmaxf(red[8 + h], red[12 + h]));
-          // power of two: exact to apply and to undo; 256 * amax' <= 448 keeps both codes in range
-          int e = 0;
-          if (amax > 0.f) {
-            frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
-            e = 8 - e;         // q * 2^(8-e) has magnitude in [128, 256)
-          }
-          const float up = ldexpf(1.0f, e);
-          q_inv_scale[h] = ldexpf(1.0f, -e);
-          const float scaled = qv[h] * up;
-          const uint32_t hi = to_e4m3(scaled);
-          const uint32_t lo = to_e4m3(scaled - from_e4m3(hi));
-          st_shared_u8(swizzled(q8_tile, h, tid), hi);
-          st_shared_u8(swizzled(q8_tile, 4 + h, tid), lo);
-        }
-      }
-      float score_scale[kGroupMax];
-      {
-        const float ks = p.k_scale[b * p.kv_heads + g] * p.scale_log2;
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) score_scale[h] = q_inv_scale[h] * ks;
       }
       fence_async_smem();
-      compute_sync();  // Q8 is complete (and red[] may be reused)
+    }
+    tc_fence_before();
+    __syncthreads();
+    // ---- MMA 1: S^T = K_tile . Q8^T
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t a_desc = umma_desc_kmajor_sw128(k_tile);
+      const uint64_t b_desc = umma_desc_kmajor_sw128(q8_tile);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) umma_ss<1, true>(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc1, ks > 0);
+      umma_commit(mma_bar);
+    }
+    if (!warp_wait(mma_bar, mma_phase, abort_flag, status, kSiteMma1)) {
+      ok = false;
+      break;
+    }
+    mma_phase ^= 1u;
+    tc_fence_after();
+    uint32_t sr[8];
+    tmem_ld_32x8(lane_base, sr);
+    tmem_ld_wait8(sr);
+    // thread = token `tid` of this iteration
+    float s[kGroupMax];
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) {
+      s[h] = (__uint_as_float(sr[h]) + __uint_as_float(sr[4 + h])) * score_scale[h];
+      if (tid >= valid) s[h] = -INFINITY;
+      float mx = s[h];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[warp * 4 + h] = mx;
+    }
+    __syncthreads();
+    float corr[kGroupMax];
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) {
+      const float mx = fmaxf(fmaxf(red[h], red[4 + h]), fmaxf(red[8 + h], red[12 + h]));
+      const float m_new = fmaxf(m_run[h], mx);
+      corr[h] = ex2_approx(m_run[h] - m_new);  // 0 on the first iteration (m_run = -inf)
+      m_run[h] = m_new;
+      const float pv = ex2_approx(s[h] - m_new);
+      l_part[h] = l_part[h] * corr[h] + pv;
+      const float scaled = pv * 256.0f;
+      const uint32_t hi = to_e4m3(scaled);
+      const uint32_t lo = to_e4m3(scaled - from_e4m3(hi));
+      st_shared_u8(swizzled(p8_tile, h, tid), hi);
+      st_shared_u8(swizzled(p8_tile, 4 + h, tid), lo);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- MMA 2: D = V_tile^T . P8^T  (A is the MN-major V tile: 8-token groups are 1024 bytes apart)
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t b_desc = umma_desc_kmajor_sw128(p8_tile);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        umma_ss<1, true>(tmem_base + 16, umma_desc_mnmajor_sw128(v_tile + ks * 32 * 128, 0, 1024), b_desc + 2 * ks,
+                         idesc2, ks > 0);
+      }
+      umma_commit(mma_bar);
+    }
+    if (!warp_wait(mma_bar, mma_phase, abort_flag, status, kSiteMma2)) {
+      ok = false;
+      break;
+    }
+    mma_phase ^= 1u;
+    tc_fence_after();
+    uint32_t dr[8];
+    tmem_ld_32x8(lane_base + 16, dr);
+    tmem_ld_wait8(dr);
+    // thread = output column d = tid
+#pragma unroll
+    for (int h = 0; h < kGroupMax; ++h) {
+      acc[h] = acc[h] * corr[h] + (__uint_as_float(dr[h]) + __uint_as_float(dr[4 + h])) * (1.0f / 256.0f);
+    }
+    // both tiles of this stage are free again: prefetch the iteration that will reuse it
+    if (tid == 0 && it + kStages < iters) issue_loads(it + kStages);
+  }
 
-      float m_run[kGroupMax], l_part[kGroupMax], acc[kGroupMax];
+  // ---- partials: l is reduced over the block; (m, l) then acc[d] per q head
+  if (ok) {
+    __syncthreads();
 #pragma unroll
-      for (int h = 0; h < kGroupMax; ++h) {
-        m_run[h] = -INFINITY;
-        l_part[h] = 0.f;
-        acc[h] = 0.f;
+    for (int h = 0; h < kGroupMax; ++h) {
+      float v = l_part[h];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) red[warp * 4 + h] = v;
+    }
+    __syncthreads();
+    for (int h = 0; h < group; ++h) {
+      const long long unit = ((long long)b * p.q_heads + g * group + h) * p.chunks + chunk;
+      float* out = p.workspace + unit * (kD + 2);
+      if (tid == 0) {
+        out[0] = m_run[h];
+        out[1] = (red[h] + red[4 + h]) + (red[8 + h] + red[12 + h]);
       }
-
-      for (int it = 0; it < iters && ok; ++it) {
-        const uint32_t fill = first_load + uint32_t(it);
-        const uint32_t stage = fill % kStages;
-        const uint32_t k_tile = k_tiles + stage * kTileBytes;
-        const uint32_t v_tile = v_tiles + stage * kTileBytes;
-        const int valid = min(kIterTokens, tokens - it * kIterTokens);
-        if (!warp_wait(kv_full + 8 * stage, (fill / kStages) & 1u, abort_flag, status, kSiteKv)) {
-          ok = false;
-          break;
-        }
-        if (valid < kIterTokens) {
-          // rows past the context end hold stale or unloaded bytes: make them zero codes so 0 * x stays 0
-          if (tid >= valid) {
-            for (int c = 0; c < 8; ++c) {
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_tile + tid * 128 + c * 16), "r"(0u) : "memory");
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + tid * 128 + c * 16), "r"(0u) : "memory");
-            }
-          }
-          fence_async_smem();
-        }
-        tc_fence_before();
-        compute_sync();
-        const bool absent = tid >= valid || ((bad_pages[stage] >> (tid >> 6)) & 1) != 0;
-        // ---- MMA 1: S^T = K_tile . Q8^T
-        if (tid == 0) {
-          tc_fence_after();
-          const uint64_t a_desc = umma_desc_kmajor_sw128(k_tile);
-          const uint64_t b_desc = umma_desc_kmajor_sw128(q8_tile);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma_ss<1, true>(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc1, ks > 0);
-          umma_commit(mma_bar);
-        }
-        if (!warp_wait(mma_bar, mma_phase, abort_flag, status, kSiteMma1)) {
-          ok = false;
-          break;
-        }
-        mma_phase ^= 1u;
-        tc_fence_after();
-        uint32_t sr[8];
-        tmem_ld_32x8(lane_base, sr);
-        tmem_ld_wait8(sr);
-        // thread = token `tid` of this iteration
-        float s[kGroupMax];
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) {
-          s[h] = (__uint_as_float(sr[h]) + __uint_as_float(sr[4 + h])) * score_scale[h];
-          if (absent) s[h] = -INFINITY;
-          float mx = s[h];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-          if (lane == 0) red[warp * 4 + h] = mx;
-        }
-        compute_sync();
-        float corr[kGroupMax];
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) {
-          const float mx = fmaxf(fmaxf(red[h], red[4 + h]), fmaxf(red[8 + h], red[12 + h]));
-          const float m_new = fmaxf(m_run[h], mx);
-          // all keys so far absent (only possible through out-of-range page ids): keep everything at zero
-          const bool none = m_new == -INFINITY;
-          corr[h] = none ? 1.f : ex2_approx(m_run[h] - m_new);  // 0 on the first iteration (m_run = -inf)
-          m_run[h] = m_new;
-          const float pv = none ? 0.f : ex2_approx(s[h] - m_new);
-          l_part[h] = l_part[h] * corr[h] + pv;
-          const float scaled = pv * 256.0f;
-          const uint32_t hi = to_e4m3(scaled);
-          const uint32_t lo = to_e4m3(scaled - from_e4m3(hi));
-          st_shared_u8(swizzled(p8_tile, h, tid), hi);
-          st_shared_u8(swizzled(p8_tile, 4 + h, tid), lo);
-        }
-        fence_async_smem();
-        tc_fence_before();
-        compute_sync();
-        // ---- MMA 2: D = V_tile^T . P8^T  (A is the MN-major V tile: 8-token groups are 1024 bytes apart)
-        if (tid == 0) {
-          tc_fence_after();
-          const uint64_t b_desc = umma_desc_kmajor_sw128(p8_tile);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            umma_ss<1, true>(tmem_base + 16, umma_desc_mnmajor_sw128(v_tile + ks * 32 * 128, 0, 1024), b_desc + 2 * ks,
-                             idesc2, ks > 0);
-          }
-          umma_commit(mma_bar);
-        }
-        if (!warp_wait(mma_bar, mma_phase, abort_flag, status, kSiteMma2)) {
-          ok = false;
-          break;
-        }
-        mma_phase ^= 1u;
-        tc_fence_after();
-        uint32_t dr[8];
-        tmem_ld_32x8(lane_base + 16, dr);
-        tmem_ld_wait8(dr);
-        // thread = output column d = tid
-#pragma unroll
-        for (int h = 0; h < kGroupMax; ++h) {
-          acc[h] = acc[h] * corr[h] + (__uint_as_float(dr[h]) + __uint_as_float(dr[4 + h])) * (1.0f / 256.0f);
-        }
-        // both tiles of this stage are free again: prefetch the iteration that will reuse it
-        if (tid == 0 && it + kStages < iters) issue_loads(it + kStages);
-      }
-      if (!ok) break;
-      loads = first_load + uint32_t(iters);
-
-      // ---- partials: l is reduced over the block; (m, l) then acc[d] per q head
-      compute_sync();
-#pragma unroll
-      for (int h = 0; h < kGroupMax; ++h) {
-        float v = l_part[h];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) red[warp * 4 + h] = v;
-      }
-      compute_sync();
-      const int used = (len + kChunkTokens - 1) / kChunkTokens;
-      if (used == 1) {
-        // the only chunk of its sequence: finish here, no partials
-        const float vs = p.v_scale[b * p.kv_heads + g];
-        for (int h = 0; h < group; ++h) {
-          const float den = (red[h] + red[4 + h]) + (red[8 + h] + red[12 + h]);
-          const float value = den > 0.f ? acc[h] / den * vs : 0.f;
-          p.o[((long long)b * p.q_heads + g * group + h) * kD + tid] = uint16_t(pack_bf16x2(value, 0.f) & 0xffffu);
-        }
-        continue;
-      }
-      for (int h = 0; h < group; ++h) {
-        const long long at = ((long long)b * p.q_heads + g * group + h) * p.chunks + chunk;
-        float* out = p.partials + at * (kD + 2);
-        if (tid == 0) {
-          out[0] = m_run[h];
-          out[1] = (red[h] + red[4 + h]) + (red[8 + h] + red[12 + h]);
-        }
-        out[2 + tid] = acc[h];
-      }
-      // ---- who finishes the last chunk of (b, g) combines them: every writer fences, one thread takes a ticket
-      __threadfence();
-      compute_sync();
-      if (tid == 0) *last_flag = atomicAdd(p.counters + 1 + bg, 1) == used - 1 ? 1 : 0;
-      compute_sync();
-      if (*last_flag != 0) {
-        __threadfence();
-        const float vs = p.v_scale[b * p.kv_heads + g];
-        for (int h = 0; h < group; ++h) {
-          // O[b, h, :] = (sum_c 2^(m_c - M) acc_c) / (sum_c 2^(m_c - M) l_c) * v_scale; the other chunks' partials were
-          // written by other SMs: read them past the L1 (ld.global.cg)
-          const float* rows = p.partials + ((long long)b * p.q_heads + g * group + h) * p.chunks * (kD + 2);
-          float m = -INFINITY;
-          for (int c = 0; c < used; ++c) m = fmaxf(m, __ldcg(rows + c * (kD + 2)));
-          float num = 0.f, den = 0.f;
-          for (int c = 0; c < used; ++c) {
-            const float mc = __ldcg(rows + c * (kD + 2));
-            const float w = mc == -INFINITY ? 0.f : exp2f(mc - m);
-            den += w * __ldcg(rows + c * (kD + 2) + 1);
-            num += w * __ldcg(rows + c * (kD + 2) + 2 + tid);
-          }
-          const float value = den > 0.f ? num / den * vs : 0.f;
-          p.o[((long long)b * p.q_heads + g * group + h) * kD + tid] = uint16_t(pack_bf16x2(value, 0.f) & 0xffffu);
-        }
-      }
-      // (the next unit's first compute_sync orders the reads of last_flag before it can be rewritten)
+      out[2 + tid] = acc[h];
     }
   }
+  if (tid == 0 && bad_page != 0) report_failure(status, kErrDeviceIndex, kSitePageId, uint32_t(bad_page) & 0x7fffffffu);
+  // the merge kernel is launched as a programmatic dependent: let it start arriving while the last CTAs drain
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (*abort_flag != 0) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -474,6 +377,48 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   }
 }
 
+// O[b, h, :] = (sum_c 2^(m_c - M) acc_c) / (sum_c 2^(m_c - M) l_c) * v_scale, rounded once to bf16.
+__global__ void decode_merge_kernel(const float* __restrict__ workspace, const int32_t* __restrict__ context_len,
+                                    const float* __restrict__ v_scale, uint16_t* __restrict__ o, int q_heads,
+                                    int kv_heads, int chunks, int max_context) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int len = max(0, min(context_len[b], max_context));
+  const int used = min(chunks, (len + kChunkTokens - 1) / kChunkTokens);
+  // launched with programmatic stream serialisation: this grid may be resident before the partial kernel has
+  // finished; the partials are valid only after this wait (inputs of the call itself are read above it)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const float* unit = workspace + ((long long)b * q_heads + h) * chunks * (kD + 2);
+  float m = -INFINITY;
+  for (int c = 0; c < used; ++c) m = fmaxf(m, unit[c * (kD + 2)]);
+  float num = 0.f, den = 0.f;
+  for (int c = 0; c < used; ++c) {
+    const float w = exp2f(unit[c * (kD + 2)] - m);
+    den += w * unit[c * (kD + 2) + 1];
+    num += w * unit[c * (kD + 2) + 2 + d];
+  }
+  const float vs = v_scale[b * kv_heads + h / (q_heads / kv_heads)];
+  const float value = used > 0 ? num / den * vs : 0.f;
+  o[((long long)b * q_heads + h) * kD + d] = uint16_t(pack_bf16x2(value, 0.f) & 0xffffu);
+}
+
+// The merge launch overlaps its own launch latency with the tail of the partial kernel (programmatic dependent launch).
+int launch_merge(const float* workspace, const int32_t* context_len, const float* v_scale, uint16_t* o, int q_heads,
+                 int kv_heads, int batch, int chunks, int max_context, cudaStream_t stream) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(q_heads), unsigned(batch), 1);
+  config.blockDim = dim3(kD, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  KRNB_CUDA(cudaLaunchKernelEx(&config, decode_merge_kernel, workspace, context_len, v_scale, o, q_heads, kv_heads, chunks,
+                               max_context));
+  return KRN_B200_OK;
+}
+
 int encode_pages(CUtensorMap* map, const void* pages, int64_t num_pages, int64_t kv_heads) {
   uint64_t dims[4] = {uint64_t(kD), uint64_t(kv_heads), uint64_t(kPage), uint64_t(num_pages)};
   uint64_t strides[3] = {uint64_t(kD), uint64_t(kD) * kv_heads, uint64_t(kD) * kv_heads * kPage};
@@ -481,13 +426,11 @@ int encode_pages(CUtensorMap* map, const void* pages, int64_t num_pages, int64_t
   return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, pages, dims, strides, box, Swizzle::k128B);
 }
 
-// Floats of split-KV partials and ints of counters a problem needs. The counter count is taken with q_heads in place
-// of kv_heads (kv_heads <= q_heads), because the workspace query of the ABI is not told kv_heads.
+// Floats of split-KV partials a problem needs: (m, l, acc[d]) per (sequence, q head, 1024-token chunk).
 long long partial_floats(int64_t batch, int64_t q_heads, int64_t max_context) {
   const long long chunks = (max_context + kChunkTokens - 1) / kChunkTokens;
-  return ((long long)batch * q_heads * chunks * (kD + 2) + 63) / 64 * 64;
+  return (long long)batch * q_heads * chunks * (kD + 2);
 }
-long long counter_ints(int64_t batch, int64_t q_heads) { return 1 + (long long)batch * q_heads; }
 
 struct DecodeArguments {
   const void *q, *k_pages, *v_pages;
@@ -519,6 +462,10 @@ int check_arguments(const DecodeArguments& a) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "max_context %lld does not fit %lld pages per sequence",
                 (long long)a.max_context, (long long)a.max_pages_per_seq);
   }
+  if (a.batch > 65535 || a.kv_heads > 65535) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "batch %lld x kv_heads %lld is not available: both are grid dimensions of at "
+                "most 65535. Instead: split the batch", (long long)a.batch, (long long)a.kv_heads);
+  }
   if (a.num_pages <= 0 || a.num_pages >= INT32_MAX || a.batch * a.q_heads > INT32_MAX / 16 || a.max_context > INT32_MAX / 2) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "num_pages %lld must be positive and extents must fit 32-bit indices",
                 (long long)a.num_pages);
@@ -529,8 +476,9 @@ int check_arguments(const DecodeArguments& a) {
   return KRN_B200_OK;
 }
 
-// Clears the counters and launches the kernel; `scratch` holds partial_floats() floats followed by counter_ints() ints.
-int launch_decode(const DecodeArguments& a, float* scratch, int sm_count, DeviceStatus* status, cudaStream_t stream) {
+// Launches the two kernels; `scratch` holds partial_floats() floats and needs no preparation (a call reads back only
+// the partials it wrote).
+int launch_decode(const DecodeArguments& a, float* scratch, DeviceStatus* status, cudaStream_t stream) {
   CUtensorMap map_k, map_v;
   if (int rc = encode_pages(&map_k, a.k_pages, a.num_pages, a.kv_heads)) return rc;
   if (int rc = encode_pages(&map_v, a.v_pages, a.num_pages, a.kv_heads)) return rc;
@@ -540,10 +488,7 @@ int launch_decode(const DecodeArguments& a, float* scratch, int sm_count, Device
   p.page_table = a.page_table;
   p.context_len = a.context_len;
   p.k_scale = a.k_scale;
-  p.v_scale = a.v_scale;
-  p.o = static_cast<uint16_t*>(a.o);
-  p.partials = scratch;
-  p.counters = reinterpret_cast<int*>(scratch + partial_floats(a.batch, a.q_heads, a.max_context));
+  p.workspace = scratch;
   p.batch = int(a.batch);
   p.q_heads = int(a.q_heads);
   p.kv_heads = int(a.kv_heads);
@@ -554,15 +499,12 @@ int launch_decode(const DecodeArguments& a, float* scratch, int sm_count, Device
   p.num_pages = int(a.num_pages);
   p.scale_log2 = a.scale_log2;
 
-  // the ticket counter and the arrival counters start every call at zero (a memset node, not an allocation)
-  KRNB_CUDA(cudaMemsetAsync(p.counters, 0, size_t(counter_ints(a.batch, a.kv_heads)) * sizeof(int), stream));
-  KRNB_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-  const long long units = (long long)p.chunks * a.batch * a.kv_heads;
-  const long long resident = 3ll * sm_count;
-  const unsigned grid = unsigned(units < resident ? units : resident);
-  decode_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_k, map_v, p, status);
+  KRNB_CUDA(cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  decode_partial_kernel<<<dim3(unsigned(p.chunks), unsigned(a.kv_heads), unsigned(a.batch)), kThreads, kSmemBytes, stream>>>(
+      map_k, map_v, p, status);
   KRNB_CUDA(cudaGetLastError());
-  return KRN_B200_OK;
+  return launch_merge(scratch, a.context_len, a.v_scale, static_cast<uint16_t*>(a.o), p.q_heads, p.kv_heads, p.batch,
+                      p.chunks, p.max_context, stream);
 }
 
 }  // namespace
@@ -570,7 +512,7 @@ int launch_decode(const DecodeArguments& a, float* scratch, int sm_count, Device
 
 extern "C" int64_t krn_b200_attn_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t d, int64_t max_context) {
   if (batch <= 0 || q_heads <= 0 || d <= 0 || max_context <= 0) return 0;
-  return (krnb::partial_floats(batch, q_heads, max_context) + krnb::counter_ints(batch, q_heads)) * 4;
+  return krnb::partial_floats(batch, q_heads, max_context) * 4;
 }
 
 extern "C" int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages, const void* v_pages,
@@ -594,8 +536,7 @@ extern "C" int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages
   DeviceContext* ctx = current_context();
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
-  return launch_decode(a, static_cast<float*>(workspace), ctx->sm_count, ctx->status_dev,
-                       static_cast<cudaStream_t>(stream_handle));
+  return launch_decode(a, static_cast<float*>(workspace), ctx->status_dev, static_cast<cudaStream_t>(stream_handle));
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -604,8 +545,7 @@ extern "C" int krn_b200_attn_decode_fp8_paged(const void* q, const void* k_pages
 // Some hosts of this library cannot call cudaMalloc at the point where they need attention: a serving loop
 // that has handed all free HBM to its KV-cache pool, a plugin running inside another runtime's memory budget,
 // or code on a path where an allocation (and the implicit synchronisation it can cause) is forbidden. For
-// them the split-KV partials and the kernel's counters live in a fixed array inside the library image instead of a
-// caller workspace. Every GPU that loads the library carries these 16 MiB until the process exits.
+// them the split-KV partials live in a fixed array inside the library image instead of a caller workspace. Every GPU that loads the library carries these 16 MiB until the process exits.
 namespace krnb {
 namespace {
 
@@ -615,12 +555,10 @@ static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
 constexpr int kScratchDevices = 64;
 std::mutex g_scratch_mutex;
 float* g_scratch_address[kScratchDevices] = {nullptr};
-int g_scratch_sm_count[kScratchDevices] = {0};
 
-// Device address of g_decode_scratch on the CURRENT device (and that device's SM count). In host code the array's
-// name is only a handle: the address a kernel may dereference comes from cudaGetSymbolAddress, once per device, with
-// that device current.
-int static_scratch(float** address, int* sm_count) {
+// Device address of g_decode_scratch on the CURRENT device. In host code the array's name is only a handle: the
+// address a kernel may dereference comes from cudaGetSymbolAddress, once per device, with that device current.
+int static_scratch(float** address) {
   int device = -1;
   KRNB_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= kScratchDevices) {
@@ -628,20 +566,17 @@ int static_scratch(float** address, int* sm_count) {
   }
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (g_scratch_address[device] == nullptr) {
-    int major = 0, sms = 0;
+    int major = 0;
     KRNB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
-    KRNB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     if (major != 10) {
       return fail(KRN_B200_ERR_UNSUPPORTED, "tcgen05 kernels is not available on this device: this library holds "
                   "sm_100a code only. Instead: run on a B200 (compute capability 10.x)");
     }
     float* resolved = nullptr;
     KRNB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&resolved), g_decode_scratch));
-    g_scratch_sm_count[device] = sms;
     g_scratch_address[device] = resolved;
   }
   *address = g_scratch_address[device];
-  *sm_count = g_scratch_sm_count[device];
   return KRN_B200_OK;
 }
 
@@ -659,19 +594,18 @@ extern "C" int krn_b200_attn_decode_fp8_paged_noalloc(const void* q, const void*
                              d, page_size, num_pages, max_pages_per_seq, max_context, scale_log2};
   if (int rc = check_arguments(a)) return rc;
   if (batch == 0) return KRN_B200_OK;
-  const long long need = partial_floats(batch, q_heads, max_context) + counter_ints(batch, q_heads);
+  const long long need = partial_floats(batch, q_heads, max_context);
   if (need > kStaticScratchFloats) {
     return fail(KRN_B200_ERR_WORKSPACE,
-                "batch %lld x q_heads %lld x %lld context chunks needs %lld scratch words; the built-in scratch holds "
+                "batch %lld x q_heads %lld x %lld context chunks needs %lld scratch floats; the built-in scratch holds "
                 "%lld (16 MiB). Use krn_b200_attn_decode_fp8_paged with a caller workspace for larger problems",
                 (long long)batch, (long long)q_heads, (long long)((max_context + kChunkTokens - 1) / kChunkTokens), need,
                 kStaticScratchFloats);
   }
   float* scratch = nullptr;
-  int sm_count = 0;
-  if (int rc = static_scratch(&scratch, &sm_count)) return rc;
+  if (int rc = static_scratch(&scratch)) return rc;
   // the status word exists only if a regular entry point created it earlier; this call never allocates one
   DeviceContext* ctx = existing_context();
   DeviceStatus* status = ctx != nullptr ? ctx->status_dev : nullptr;
-  return launch_decode(a, scratch, sm_count, status, static_cast<cudaStream_t>(stream_handle));
+  return launch_decode(a, scratch, status, static_cast<cudaStream_t>(stream_handle));
 }

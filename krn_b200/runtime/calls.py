@@ -30,6 +30,8 @@ def _pointer(tensor: Any) -> int:
 def _pitch(tensor: Any) -> int:
     """Row pitch in elements of a rank-2 tensor whose last axis is contiguous."""
     strides = tuple(tensor.stride()) if callable(getattr(tensor, "stride", None)) else tuple(tensor.strides)
+    if len(strides) == 2 and 0 in tuple(tensor.shape):
+        return max(1, int(tensor.shape[1]))  # an empty tensor has no meaningful strides
     if len(strides) != 2 or (tensor.shape[1] > 1 and strides[1] != 1):
         raise ValueError("expected a rank-2 tensor with a contiguous last axis")
     return int(strides[0]) if tensor.shape[0] > 1 else max(int(strides[0]), int(tensor.shape[1]))

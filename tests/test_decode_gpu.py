@@ -81,8 +81,9 @@ def test_context_lengths_are_clamped_to_max_context(cuda) -> None:
 
 
 def test_page_ids_outside_the_pool_are_never_fetched(cuda) -> None:
-    """Ids of num_pages and -1: in table slots past the context they are not looked at; inside the context their keys
-    count as absent (the result equals that of the sequence without those 64 tokens) and the status word says so."""
+    """Ids of num_pages and -1: in table slots past the context they are not looked at; inside the context the page is
+    not fetched — its 64 tokens read as zero codes, exactly as if the table pointed at a page of zeros — and the status
+    word says so."""
     from krn_b200.runtime import native
 
     q, kp, vp, table, lens, ks, vs = o.config_decode(batch=3, q_heads=8, kv_heads=2, d=128, low=300, high=1400, seed=10)
@@ -95,17 +96,16 @@ def test_page_ids_outside_the_pool_are_never_fetched(cuda) -> None:
     np.testing.assert_array_equal(run(cuda, q, kp, vp, unused, lens, ks, vs), clean)
     assert native.device_status()[0] == 0
 
-    # sequence 0 loses its third page, sequence 2 its first: full pages, so dropping them from the table and shortening
-    # the context by 64 describes the same set of keys
-    broken, repaired, shorter = table.copy(), table.copy(), lens.copy()
+    # sequence 0 loses its third page, sequence 2 its first; the oracle sees a pool with one more page, all zero codes
+    broken, zeroed = table.copy(), table.copy()
     broken[0, 2], broken[2, 0] = kp.shape[0], -1
-    repaired[0, 2:-1], repaired[2, 0:-1] = table[0, 3:], table[2, 1:]
-    shorter[0] -= 64
-    shorter[2] -= 64
+    zeroed[0, 2] = zeroed[2, 0] = kp.shape[0]
+    pad = np.zeros((1,) + kp.shape[1:], np.uint8)
     got = run(cuda, q, kp, vp, broken, lens, ks, vs)
     code, site, _ = native.device_status()  # reads and clears the word
     assert code == native.ERR_DEVICE_INDEX and site == 36
-    want = o.bf16_values(o.decode_fp8_paged(q, kp, vp, repaired, shorter, ks, vs, scale_log2=scale))
+    want = o.bf16_values(o.decode_fp8_paged(q, np.concatenate([kp, pad]), np.concatenate([vp, pad]), zeroed, lens, ks, vs,
+                                            scale_log2=scale))
     assert np.isfinite(got).all()
     assert o.rel_frobenius(got, want) < 1e-2
 
@@ -134,4 +134,4 @@ def test_refusals_and_workspace(cuda) -> None:
     small = torch.empty(16, device="cuda", dtype=torch.uint8)
     with pytest.raises(Exception, match="KRN_B200_ERR_WORKSPACE"):
         calls.attention_decode_fp8_paged(*args, out, 1.0, int(table.shape[1]) * 64, small)
-    assert calls.decode_workspace_bytes(2, 4, 128, 128) == (1088 + 1 + 2 * 4) * 4  # partials (64-word multiple) + counters
+    assert calls.decode_workspace_bytes(2, 4, 128, 128) == 2 * 4 * 1 * 130 * 4
