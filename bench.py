@@ -144,7 +144,7 @@ class Workload:
         return f"{size} would fit the 126 MB L2: steps rotate through {copies} copies ({copies * set_bytes / 2**20:.0f} MiB)"
 
     def peak(self, peaks: dict) -> tuple[float, str]:
-        return peaks["bf16_tflops"], "burst (cuBLAS bf16 8192^3)"
+        return peaks["bf16_tflops_sustained"], "sustained cuBLAS bf16 8192^3 (seconds-long loop under the power cap)"
 
 
 class GemmBf16(Workload):
@@ -315,7 +315,7 @@ class GemmFp8(Workload):
         return 2.0 * self.m * self.n_local * self.k
 
     def peak(self, peaks: dict) -> tuple[float, str]:
-        return 2.0 * peaks["bf16_tflops"], "2 x burst cuBLAS bf16 (no FP8 peak was measured on this pool)"
+        return 2.0 * peaks["bf16_tflops_sustained"], "2 x sustained cuBLAS bf16 (no FP8 peak was measured on this pool)"
 
     def step(self, calls) -> None:
         stream = self.torch.cuda.current_stream()
@@ -715,18 +715,22 @@ class Harness:
         kernel.sort()
         kernel_ms = kernel[len(kernel) // 2]
         achieved = workload.scale(workload.kernel_work(), kernel_ms)
+        best = workload.scale(workload.kernel_work(), kernel[0])
         peak, peak_note = workload.peak(self.peaks)
         roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit,
                     "frac": achieved / peak,
                     "traffic": None if args.size or self.world > 1 else NCU_TRAFFIC_BYTES[workload.name],
                     "peak_kind": f"{self.peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
         if workload.bound == "tensor":
+            # `achieved` is the median of a run of back-to-back launches that lasts long enough for the power cap to
+            # settle the clock, so its denominator is the cuBLAS figure measured the same way (sustained); the best trial
+            # (launches on a cool part) is set against the cuBLAS best-of-10 burst figure
             factor = 2.0 if workload.dtype.startswith("fp8") else 1.0
-            sustained = factor * self.peaks["bf16_tflops_sustained"]
-            roofline["frac_of_sustained_peak"] = achieved / sustained
-            roofline["applies"] = ("sustained: the timed region is a seconds-long run of back-to-back launches under the "
-                                   "power cap; `frac` (burst denominator) is the stricter figure and is the one reported")
+            burst = factor * self.peaks["bf16_tflops"]
+            roofline["burst"] = {"achieved": best, "peak": burst, "frac": best / burst,
+                                 "note": "best trial over the burst (best-of-10) cuBLAS figure"}
             roofline["frac_of_nominal_dense_peak"] = achieved / (4500.0 if factor == 2.0 else 2250.0)
+            roofline["best_frac_of_nominal_dense_peak"] = best / (4500.0 if factor == 2.0 else 2250.0)
 
         record = {"metric": workload.metric, "value": value, "unit": workload.unit, "ms_per_step": ms_per_step,
                   "trials": len(per_step), "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1],
