@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8 added */
+#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8 and krn_b200_gemm_mxfp8_tn added */
 
 /* status codes */
 #define KRN_B200_OK 0
@@ -146,6 +146,21 @@ int krn_b200_gemm_tn_gather(int ab_type, int c_type, const void* a, const void* 
 int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa, const void* b, const float* sb,
                                      void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
                                      int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream);
+
+/* C[M,N] = sum over 32-wide K blocks kb of  2^(sa[m,kb] - 127) * 2^(sb[n,kb] - 127) * (A8[m, kb] . B8[n, kb]):
+ * the product of two matrices in the reference's MXFP8 block format — e4m3fn codes with one e8m0 (power-of-two) scale
+ * byte per 1 x 32 block of a row (src/krn/data/formats.py:138-144; `QMatrix[MXFP8]`, src/krn/frontend/memory.py:255-269,
+ * whose `@` the reference declares and does not implement, :173-193). The scale factors are operands of the tensor-core
+ * instruction itself (tcgen05.mma kind::mxf8f6f4.block_scale reads them from tensor memory): nothing is dequantised and
+ * no partial sum is rescaled outside the unit.
+ *   a, b    e4m3fn codes, K-major: a [M, K], b [N, K]; lda / ldb in elements, multiples of 16
+ *   sa, sb  e8m0 bytes: sa [M, K / 32], sb [N, K / 32]; ldsa / ldsb row pitches in BYTES; addresses and pitches
+ *           multiples of 4 (multiples of 16 let a row's scales of four K steps come in one load)
+ *   K       a multiple of 128 (four scale blocks per step); M, N ragged as in krn_b200_gemm_tn
+ *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
+int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c, int64_t m,
+                           int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                           void* stream);
 
 /* The block-scaled FP8 product sharded by output columns with the all-gather of the columns done by the kernel's
  * epilogue, exactly as krn_b200_gemm_tn_gather does for the 16-bit product: rank `rank` multiplies A by ITS rows of B

@@ -14,7 +14,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUTPUT = HERE.parent / "libkrn_b200.so"
-SOURCES = ("host.cu", "gemm_tn.cu", "gemm_fp8.cu", "attn_fwd.cu", "attn_decode.cu", "scatter.cu")
+SOURCES = ("host.cu", "gemm_tn.cu", "gemm_fp8.cu", "gemm_mxfp8.cu", "attn_fwd.cu", "attn_decode.cu", "scatter.cu")
 FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC")
 
 

@@ -1,0 +1,435 @@
+// MXFP8 tile product with the block scales applied BY the tensor cores:
+//   C[m,n] = sum over 32-wide K blocks kb of  2^(sa[m,kb] - 127) * 2^(sb[n,kb] - 127) * (A8[m, kb-block] . B8[n, kb-block])
+// A8, B8 are e4m3fn codes (K-major), sa / sb one e8m0 byte per 1 x 32 block: the reference's `MXFP8` block format
+// (src/krn/data/formats.py:138-144; `QMatrix` / `QTile` carry it as signatures only, src/krn/frontend/memory.py:173-193,
+// 255-269). tcgen05.mma kind::mxf8f6f4.block_scale takes the scale factors as operands of the instruction — "a
+// block-scaled MMA" in the literal sense — so nothing is dequantised and no partial sum leaves tensor memory before the
+// last K block.
+//
+// Roles per CTA (256 threads, one 128 x 256 output tile at a time, persistent over tiles):
+//   warp 0      TMA producer: A (128 rows) and B (256 rows) tiles of 128 codes per row into a 4-stage ring
+//   warp 1      MMA issuer: per K block of 128 codes, copies that block's scale factors from shared memory into tensor
+//               memory (tcgen05.cp, 32x128b.warpx4: one 512-byte group per 128 rows) and issues four K = 32
+//               instructions whose descriptors select the scale byte of their 32-wide sub-block
+//   warps 2-3   scale loaders: fetch, four K blocks at a time, the 16 scale bytes of every row of the tile (one 16-byte
+//               load per row) and lay them out in shared memory the way tcgen05.cp expects a 128-row group:
+//               byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block
+//   warps 4-7   epilogue: tensor memory -> registers -> output type -> swizzled staging -> TMA store
+//
+// Tensor memory (512 columns): 256 accumulator columns, then 4 columns of A scales and 8 of B scales. One accumulator
+// only — two would not leave room for the scales — so the epilogue's tensor-memory reads (not its stores) are not
+// overlapped with the next tile's products: about 5 % of a tile at K = 8192.
+//
+// The scale-factor columns are rewritten for every K block while earlier products may still be in flight; tcgen05.cp
+// and tcgen05.mma issued by one thread execute in issue order, which is what makes that safe.
+#include "gemm_common.cuh"
+
+namespace krnb {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 128;          // codes per stage row = four 32-wide scale blocks
+constexpr int kThreads = 256;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * 128;
+constexpr int kBBytes = kBN * 128;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kScaleChunk = 4;                          // K blocks of scales per ring slot (16 scale bytes per row)
+constexpr int kScaleBlockBytes = 512 + 2 * 512;         // one K block: the A group, then two B groups of 128 rows
+constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
+constexpr int kEpilogueBytes = 4 * 4096;                // per epilogue warp: one 32-row x 128-byte store box
+constexpr int kSmemBytes = kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
+constexpr int kTmemColumns = 512;
+constexpr int kTmemScaleA = 256;                        // column of the A scale factors (4 columns)
+constexpr int kTmemScaleB = 260;                        // column of the B scale factors (8 columns)
+static_assert(kSmemBytes <= 232448, "shared memory budget");
+
+struct MxScales {
+  const uint8_t* sa;  // [M, K / 32] e8m0
+  const uint8_t* sb;  // [N, K / 32] e8m0
+  long long ldsa, ldsb;  // row pitches in bytes
+  int vector_ok;         // both addresses and pitches are multiples of 16: a row's four K blocks come in one load
+};
+
+enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
+            kSiteScaleEmpty = 46 };
+
+// Instruction descriptor of kind::mxf8f6f4.block_scale: B scale id [4,6), A format [7,10), B format [10,13), majors 15 /
+// 16, N / 8 at [17,23), scale format (1 = e8m0) at 23, M / 16 at [24,29), A scale id [29,31). The scale id picks which
+// of the four bytes of a scale-factor column belongs to this instruction's 32-wide K sub-block.
+__device__ __forceinline__ uint32_t mx_idesc(uint32_t sub_block) {
+  return (sub_block << 4) | (kFmtE4M3 << 7) | (kFmtE4M3 << 10) | (uint32_t(kBN >> 3) << 17) | (1u << 23) |
+         (uint32_t(kBM >> 4) << 24) | (sub_block << 29);
+}
+
+// D[tmem] (+)= (A * scale_a) * (B * scale_b): A, B shared-memory descriptors, scales in tensor memory. One thread.
+__device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                        uint32_t scale_a_tmem, uint32_t scale_b_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+      " tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%5], [%6], p;\n}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+      : "memory");
+}
+
+// 512 bytes of shared memory (32 rows of 16 bytes, unswizzled: 8-row groups 128 bytes apart) -> 4 tensor-memory columns,
+// the same 32 x 16 bytes into each of the four 32-lane quarters.
+__device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  desc |= static_cast<uint64_t>(128 >> 4) << 32;               // stride between 8-row groups
+  desc |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_column), "l"(desc) : "memory");
+}
+
+template <typename OutT, bool OUT_BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_c, Problem p, MxScales scales, DeviceStatus* status) {
+  constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
+  constexpr int kChunks = kBN / kChunkCols;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t stages_addr = base;
+  const uint32_t scale_addr = base + kStages * kStageBytes;
+  const uint32_t epilogue_addr = scale_addr + 2 * kScaleSlotBytes;
+  uint8_t* tail = smem + kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes;
+  const uint32_t full_bar = smem_u32(tail);                  // [kStages]
+  const uint32_t empty_bar = full_bar + 8 * kStages;         // [kStages]
+  const uint32_t scale_full_bar = empty_bar + 8 * kStages;   // [2]
+  const uint32_t scale_empty_bar = scale_full_bar + 16;      // [2]
+  const uint32_t tmem_full_bar = scale_empty_bar + 16;
+  const uint32_t tmem_empty_bar = tmem_full_bar + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 6));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = p.k / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(scale_full_bar + 8 * s, 2);   // the two loader warps
+      mbar_init(scale_empty_bar + 8 * s, 1);  // the issuing thread's commit
+    }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_slot), kTmemColumns);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stages_addr + stage * kStageBytes;
+          mbar_arrive_expect_tx(full_bar + 8 * stage, kStageBytes);
+          tma_load_2d(a_dst, &map_a, kb * kBK, tm * kBM, full_bar + 8 * stage);
+          tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, tn * kBN, full_bar + 8 * stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
+      const uint32_t desc_hi = uint32_t(desc0 >> 32);
+      uint32_t a_lo = uint32_t(desc0);
+      int stage = 0;
+      uint32_t phase = 0, chunk = 0, iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+        // the single accumulator must have been read out by the epilogue of the previous tile
+        if (!mbar_wait(tmem_empty_bar, (iter & 1u) ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t slot = chunk & 1u;
+          const int in_chunk = kb & (kScaleChunk - 1);
+          if (in_chunk == 0 &&
+              !mbar_wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, abort_flag, status, kSiteMmaScale)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
+          scales_to_tmem(tmem_base + kTmemScaleA, block);
+          scales_to_tmem(tmem_base + kTmemScaleB, block + 512);
+          scales_to_tmem(tmem_base + kTmemScaleB + 4, block + 1024);
+          const uint32_t b_lo = a_lo + (kABytes >> 4);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_mx(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks), tmem_base + kTmemScaleA,
+                    tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar + 8 * stage);
+          if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) {
+            umma_commit(scale_empty_bar + 8 * slot);
+            ++chunk;
+          }
+          a_lo += kStageBytes >> 4;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+            a_lo = uint32_t(desc0);
+          }
+        }
+        if (!ok) break;
+        umma_commit(tmem_full_bar);
+      }
+    }
+  } else if (warp < 4) {
+    // ---------------------------------------------------------------- scale loaders (64 threads)
+    // Per ring slot: the 16 scale bytes (four K blocks) of the tile's 128 A rows and 256 B rows — 384 rows, six per
+    // thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
+    // group. Rows beyond the matrix get the code of 2^0 (their codes are zero-filled by TMA, the product stays zero).
+    const int tid = int(threadIdx.x) - 64;
+    uint32_t chunk = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk) {
+        const uint32_t slot = chunk & 1u;
+        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, ((chunk >> 1) & 1u) ^ 1u, abort_flag, status,
+                                               kSiteScaleEmpty))) {
+          ok = false;
+          break;
+        }
+        uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
+        const int blocks_here = min(kScaleChunk, num_kb - kb0);
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
+          const bool is_a = r < kBM;
+          const int local = is_a ? r : r - kBM;
+          const long long row = is_a ? (long long)tm * kBM + local : (long long)tn * kBN + local;
+          const bool live = row < (is_a ? p.m : p.n);
+          uint32_t w[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+          if (live) {
+            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 4;
+            if (blocks_here == kScaleChunk && scales.vector_ok) {
+              const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+              w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+            } else {
+              for (int j = 0; j < blocks_here; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
+            }
+          }
+          const int group = is_a ? 0 : 1 + local / 128;
+          const int in_group = local & 127;
+          uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
+#pragma unroll
+          for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
+        }
+        fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(scale_full_bar + 8 * slot);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int quarter = warp & 3;  // the 32-lane slice of tensor memory this warp may read
+    const uint32_t buffer = epilogue_addr + quarter * 4096;
+    uint32_t iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      const int row0 = tm * kBM + quarter * 32;
+      const int col0 = tn * kBN;
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar, iter & 1u, abort_flag, status, kSiteEpilogueFull))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
+        const int col = col0 + chunk * kChunkCols;
+        const bool live = row0 < p.m && col < p.n;  // warp-uniform
+        uint32_t packed[32];
+        if constexpr (sizeof(OutT) == 4) {
+          tmem_ld_32x32(t_row + chunk * kChunkCols, packed);
+          tmem_ld_wait(packed);
+        } else {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
+          tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
+          tmem_ld_wait(lo, hi);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if constexpr (OUT_BF16) {
+              packed[i] = pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[16 + i] = pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+            } else {
+              packed[i] = pack_f16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[16 + i] = pack_f16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+            }
+          }
+        }
+        if (chunk == kChunks - 1) {
+          // the accumulator has been read completely: hand it back before the last stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty_bar);
+        }
+        if (live) {
+          if (lane == 0) tma_store_wait_read<0>();  // the previous store has read this buffer
+          __syncwarp();
+          const uint32_t row_addr = buffer + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
+                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                         : "memory");
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_c, col, row0, buffer);
+            tma_store_commit();
+          }
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    // abandoned: give this CTA's own copies in flight time to land before shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemColumns);
+  }
+}
+
+template <typename OutT, bool OUT_BF16>
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
+           MxScales scales, cudaStream_t stream) {
+  auto kernel = gemm_mxfp8_kernel<OutT, OUT_BF16>;
+  KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p, scales, ctx->status_dev);
+  KRNB_CUDA(cudaGetLastError());
+  return KRN_B200_OK;
+}
+
+}  // namespace
+}  // namespace krnb
+
+extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c,
+                                      int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa,
+                                      int64_t ldsb, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
+  }
+  if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent");
+  if (m == 0 || n == 0) return KRN_B200_OK;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
+  }
+  if (k == 0 || k % kBK != 0) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "MXFP8 product with K = %lld is not available on sm_100a: the kernel consumes "
+                "four 32-wide scale blocks per step. Instead: pad K to a multiple of 128 with zero codes", (long long)k);
+  }
+  if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  const int64_t blocks_k = k / 32;
+  if (ldc < n || lda < k || ldb < k || ldsa < blocks_k || ldsb < blocks_k) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
+  }
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "TMA needs 16-byte aligned base addresses and row pitches");
+  }
+  if (reinterpret_cast<uintptr_t>(sa) % 4 != 0 || reinterpret_cast<uintptr_t>(sb) % 4 != 0 || ldsa % 4 != 0 || ldsb % 4 != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "scale matrices need 4-byte aligned addresses and row pitches (the four "
+                "scale bytes of a 128-wide K step are fetched as one word)");
+  }
+  DeviceContext* ctx = current_context();
+  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
+  if (int rc = require_sm100(ctx)) return rc;
+
+  Problem p;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.tiles_m = int((m + kBM - 1) / kBM);
+  p.tiles_n = int((n + kBN - 1) / kBN);
+  p.b_kn = 0;
+  MxScales scales = {sa, sb, ldsa, ldsb, (aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0) ? 1 : 0};
+
+  CUtensorMap map_a, map_b, map_c;
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(lda)};
+    uint32_t box[2] = {128, uint32_t(kBM)};
+    if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
+    uint64_t strides[1] = {uint64_t(ldb)};
+    uint32_t box[2] = {128, uint32_t(kBN)};
+    if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  if (c_type == KRN_B200_F32) return launch<float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
+  return launch<uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+}

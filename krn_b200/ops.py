@@ -8,8 +8,12 @@ import math
 from dataclasses import dataclass
 from typing import Any
 
+import numpy as np
+
+from krn_b200.errors import TargetError
+from krn_b200.frontend.types import f8e4m3fn
 from krn_b200.runtime import calls
-from krn_b200.runtime.device import DeviceTensor, _raw
+from krn_b200.runtime.device import DeviceTensor, _raw, default_device
 
 
 def _stream(stream: Any):
@@ -31,21 +35,94 @@ def matmul(a: Any, b: Any, out: Any, stream: Any = None) -> Any:
 
 @dataclass(frozen=True)
 class QMatrix:
-    """A block-scaled FP8 matrix on the device: e4m3fn `codes` (rows, K) and fp32 `scales` with one scale per
-    `block` (1x128 for activations, 128x128 for weights) — the wire format the reference sketches as
-    `QMatrix[FP8FN]` (src/krn/frontend/memory.py:257-269)."""
+    """A block-scaled matrix on the device, with the fields of the reference's `QMatrix[F]` struct
+    (src/krn/frontend/memory.py:255-269): the block format `fmt` (a `krn_b200.formats.BlockFormat`: `FP8FN()`,
+    `FP8FNWeights()` or `MXFP8()`), the logical `shape`, the `codes` (one byte per element, (rows, K), K contiguous —
+    blocks run along the contraction axis), the `scales` (f32 for the FP8FN formats, e8m0 bytes for MXFP8; one per
+    block) and an optional per-tensor `tensor_scale` (used by formats that define one; none of the three here does)."""
 
+    fmt: Any
+    shape: tuple[int, int]
     codes: Any
     scales: Any
-    block: tuple[int, int]
+    tensor_scale: Any = None
+
+    @property
+    def block(self) -> tuple[int, int]:
+        return self.fmt.block
+
+
+def _e4m3_codes(values: np.ndarray) -> np.ndarray:
+    """e4m3fn codes of float32 values: nearest, ties to even, saturating at 448 — the rule of the reference's
+    `reference_encode` (src/krn/compiler/narrow.py:94-105). `ml_dtypes` rounds the same way but does not saturate, so
+    values are clipped first."""
+    import ml_dtypes
+
+    clipped = np.clip(values.astype(np.float32), -448.0, 448.0)
+    return clipped.astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
+
+
+def quantize_host(values: np.ndarray, fmt: Any) -> tuple[np.ndarray, np.ndarray]:
+    """(codes, scales) of a float32 host matrix (rows, K) in block format `fmt`, on the host.
+
+    FP8FN / FP8FNWeights: f32 scale = block absmax / 448 (1 for a block of zeros), codes = e4m3(x / scale).
+    MXFP8: e8m0 scale byte of 2^(floor(log2 absmax) - 8) per 1 x 32 block (the OCP MX floor rule the format names, 8
+    being the exponent of the largest e4m3 value), codes = e4m3(x / scale)."""
+    from krn_b200 import formats
+
+    values = np.ascontiguousarray(values, np.float32)
+    rows, cols = values.shape
+    br, bc = fmt.block
+    if fmt.elem != formats.E4M3FN or rows % br or cols % bc:
+        raise ValueError(f"cannot quantize a {rows} x {cols} matrix to {fmt.name}: e4m3fn elements in whole {br} x {bc} blocks")
+    blocks = values.reshape(rows // br, br, cols // bc, bc)
+    absmax = np.abs(blocks).max(axis=(1, 3))
+    if fmt.scale == formats.E8M0:
+        exponent = np.where(absmax > 0, np.floor(np.log2(np.where(absmax > 0, absmax, 1.0))) - 8, 0)
+        exponent = np.clip(exponent, -127, 127).astype(np.int32)
+        scale = np.exp2(exponent.astype(np.float32))
+        stored = (exponent + 127).astype(np.uint8)
+    elif fmt.scale == formats.FP32:
+        scale = np.where(absmax > 0, absmax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+        stored = scale
+    else:
+        raise ValueError(f"no quantizer for the scale format of {fmt.name}")
+    codes = _e4m3_codes((blocks / scale[:, None, :, None]).reshape(rows, cols))
+    return codes, np.ascontiguousarray(stored)
+
+
+def quantize(values: np.ndarray, fmt: Any, device: Any = None) -> QMatrix:
+    """Convert a float32 host matrix (rows, K) to `fmt` (see `quantize_host`) and place it on the device — what the
+    reference's `Resolution.quantize(weights) -> QMatrix[F]` is declared to do (src/krn/frontend/precision.py:43-45)."""
+    device = device or default_device()
+    codes, stored = quantize_host(values, fmt)
+    return QMatrix(fmt, tuple(values.shape), device.to_device(codes, f8e4m3fn), device.to_device(stored))
+
+
+def matmul_q(a: QMatrix, b: QMatrix, out: Any, stream: Any = None) -> Any:
+    """out[M, N] = a @ b^T for two block-scaled matrices whose blocks run along K (both stored (rows, K)) — the product
+    the reference declares as `QTile.__matmul__` (src/krn/frontend/memory.py:173-193). Two pairings have kernels:
+    FP8FN activations (1 x 128 f32 scales) with FP8FNWeights (128 x 128 f32 scales), whose partial sums are scaled as they
+    are accumulated, and MXFP8 with MXFP8, whose scales the tensor cores apply themselves."""
+    from krn_b200 import formats
+
+    if a.shape[1] != b.shape[1]:
+        raise ValueError(f"contraction lengths differ: {a.shape} @ {b.shape}^T")
+    if isinstance(a.fmt, formats.MXFP8) and isinstance(b.fmt, formats.MXFP8):
+        calls.gemm_mxfp8_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
+    elif a.fmt.block == (1, 128) and b.fmt.block == (128, 128) and a.fmt.scale == formats.FP32 and b.fmt.scale == formats.FP32:
+        calls.gemm_fp8_blockscaled_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
+    else:
+        raise TargetError(f"the product {a.fmt.name} @ {b.fmt.name}", "sm_100a", "no prebuilt kernel multiplies this pair "
+                          "of block formats", "use FP8FN activations with FP8FNWeights, or MXFP8 with MXFP8")
+    return out
 
 
 def matmul_fp8_blockscaled(a: QMatrix, b: QMatrix, out: Any, stream: Any = None) -> Any:
     """out = sum over 128-wide K blocks of sa * sb * (a8 @ b8^T); a has 1x128 scales, b 128x128 scales."""
     if a.block != (1, 128) or b.block != (128, 128):
         raise ValueError("matmul_fp8_blockscaled takes 1x128-scaled activations and 128x128-scaled weights")
-    calls.gemm_fp8_blockscaled_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
-    return out
+    return matmul_q(a, b, out, stream)
 
 
 def attention(q: Any, k: Any, v: Any, out: Any, *, causal: bool = False, scale: float | None = None,
@@ -77,5 +154,5 @@ def decode_attention(q: Any, k_pages: Any, v_pages: Any, page_table: Any, contex
     return out
 
 
-__all__ = ["DeviceTensor", "QMatrix", "attention", "decode_attention", "decode_attention_workspace", "matmul_fp8_blockscaled",
-           "matmul_nt"]
+__all__ = ["DeviceTensor", "QMatrix", "attention", "decode_attention", "decode_attention_workspace", "matmul", "matmul_fp8_blockscaled",
+           "matmul_nt", "matmul_q", "quantize", "quantize_host"]

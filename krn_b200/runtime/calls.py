@@ -149,6 +149,22 @@ def gemm_fp8_blockscaled_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: An
     native.check(status, "block-scaled FP8 tile matrix product")
 
 
+def gemm_mxfp8_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: Any = None) -> None:
+    """c = sum over 32-wide K blocks of 2^(sa - 127) * 2^(sb - 127) * (a8 @ b8^T): a [M, K], b [N, K] e4m3 codes, sa [M, K/32]
+    and sb [N, K/32] e8m0 bytes (uint8). The tensor cores apply the scales themselves."""
+    (m, k), (n, kb) = a.shape, b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    if tuple(sa.shape) != (m, k // 32) or tuple(sb.shape) != (n, k // 32) or k % 32:
+        raise ValueError(f"scale shapes {tuple(sa.shape)}, {tuple(sb.shape)} do not match 1x32 blocks of K = {k}")
+    if "uint8" not in str(sa.dtype) or "uint8" not in str(sb.dtype):
+        raise TypeError("MX scales are e8m0 bytes: pass uint8 tensors")
+    status = native.library().krn_b200_gemm_mxfp8_tn(
+        _type_of(c), _pointer(a), _pointer(sa), _pointer(b), _pointer(sb), _pointer(c), m, n, k, _pitch(a), _pitch(b),
+        _pitch(c), _pitch(sa), _pitch(sb), _stream(stream))
+    native.check(status, "MXFP8 tile matrix product")
+
+
 def gemm_fp8_blockscaled_tn_gather(a: Any, sa: Any, b_local: Any, sb_local: Any, c_pointers: list[int], rank: int,
                                    n_local: int, ldc: int, c_type: int, stream: Any = None,
                                    sync_pointers: list[int] | None = None, epoch: int = 0) -> None:

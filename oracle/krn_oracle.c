@@ -14,8 +14,11 @@
  *     tests/frontend/test_tile_ops.py:130-154).
  *   - e4m3fn decode: PINNED against the independent 256-entry table of
  *     tests/compiler/test_tensor_cores.py:200-216.
- *   - block-scaled FP8 product, grouped-query / batched attention, paged FP8 decode: PARITY UNPINNED —
- *     the reference has neither an implementation nor a test; the definitions here are ours.
+ *   - e5m2 decode and mixed e4m3 / e5m2 pair products: PINNED against the same tests (seed-81 code draw, all four
+ *     pairings, tests/compiler/test_tensor_cores.py:146,219-239).
+ *   - block-scaled FP8 product, MXFP8 product, grouped-query / batched attention, paged FP8 decode: PARITY UNPINNED —
+ *     the reference has neither an implementation nor a test; the definitions here are ours (the MXFP8 FORMAT is the
+ *     reference's, src/krn/data/formats.py:138-144, and its value tables are pinned).
  *
  * Build: see oracle/Makefile (gcc -O2 -march=native -ffp-contract=off -fwrapv -fPIC -shared, the
  * reference's clang flags, src/krn/runtime/cpu.py:48-51, src/krn/runtime/compile_options.py:279-295).
@@ -280,6 +283,51 @@ void krn_oracle_gemm_fp8_blockscaled(int c_type, const uint8_t* a, const float* 
       float sai = sa[i * ldsa + kb];
       for (int64_t j = 0; j < n; ++j) {
         float scale = sai * sb[(j / 128) * ldsb + kb];
+        float scaled = scale * part[j];
+        total[j] = total[j] + scaled;
+      }
+    }
+    for (int64_t j = 0; j < n; ++j) store_from_f32(c, c_type, i * ldc + j, total[j]);
+  }
+  free(bt);
+  free(part);
+  free(total);
+}
+
+/* ---- MXFP8 product (the reference's MXFP8 format; its product is declared, not implemented: parity unpinned) ---- */
+
+/* e8m0 scale byte -> value: 2^(code - 127), 0xFF is NaN (src/krn/data/formats.py:98: 8 exponent bits, no mantissa, no
+ * sign, bias 127, exponent field 0 is 2^-127 and not zero). */
+float krn_oracle_e8m0_decode(uint8_t code) { return code == 0xFF ? NAN : ldexpf(1.0f, (int)code - 127); }
+
+/* C[i,j] = sum over 32-wide K blocks kb of (2^(sa[i,kb]-127) * 2^(sb[j,kb]-127)) * P_kb[i,j], P_kb the fma chain of the
+ * decoded e4m3 codes over the block starting from +0.0f; the scaled partials are added in kb order in f32. The product
+ * of two powers of two and its multiplication into P_kb are exact (barring overflow), so only the two accumulations
+ * round. Rows [row_begin, row_end). */
+void krn_oracle_gemm_mxfp8(int c_type, const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb, void* c,
+                           int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa,
+                           int64_t ldsb, int64_t row_begin, int64_t row_end) {
+  (void)m;
+  float table[256];
+  for (int i = 0; i < 256; ++i) table[i] = krn_oracle_e4m3_decode((uint8_t)i);
+  float* bt = aligned_alloc(64, ((size_t)(k > 0 ? k : 1) * n * 4 + 63) / 64 * 64);
+  float* part = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  float* total = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  for (int64_t kk = 0; kk < k; ++kk)
+    for (int64_t j = 0; j < n; ++j) bt[kk * n + j] = table[b[j * ldb + kk]];
+  for (int64_t i = row_begin; i < row_end; ++i) {
+    for (int64_t j = 0; j < n; ++j) total[j] = 0.0f;
+    for (int64_t k0 = 0, kb = 0; k0 < k; k0 += 32, ++kb) {
+      int64_t k1 = k0 + 32 < k ? k0 + 32 : k;
+      for (int64_t j = 0; j < n; ++j) part[j] = 0.0f;
+      for (int64_t kk = k0; kk < k1; ++kk) {
+        float av = table[a[i * lda + kk]];
+        const float* brow = bt + kk * n;
+        for (int64_t j = 0; j < n; ++j) part[j] = __builtin_fmaf(av, brow[j], part[j]);
+      }
+      float sai = krn_oracle_e8m0_decode(sa[i * ldsa + kb]);
+      for (int64_t j = 0; j < n; ++j) {
+        float scale = sai * krn_oracle_e8m0_decode(sb[j * ldsb + kb]);
         float scaled = scale * part[j];
         total[j] = total[j] + scaled;
       }

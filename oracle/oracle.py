@@ -51,13 +51,14 @@ def lib() -> ctypes.CDLL:
         handle.krn_oracle_gemm_blocks.argtypes = [i32, i32, i32, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i32, i32, i32, i64, i64]
         handle.krn_oracle_gemm_fast.argtypes = [i32, i32, i32, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_fp8_blockscaled.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
+        handle.krn_oracle_gemm_mxfp8.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_flash_attention.argtypes = [i32, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i32, f32, i32, i32, i32, i64, i64]
         handle.krn_oracle_decode_fp8_paged.argtypes = [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i64, i32, i32, i64, f32, i64, i64]
         handle.krn_oracle_e4m3_encode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_e4m3_decode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_bf16_round_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_matmul_epilogue.argtypes = [i32, ptr, ptr, ptr, i64, i64, i32]
-        for name in ("matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
+        for name in ("gemm_mxfp8", "matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
                      "e4m3_encode_array", "e4m3_decode_array", "bf16_round_array"):
             getattr(handle, f"krn_oracle_{name}").restype = None
         _LIB = handle
@@ -171,6 +172,39 @@ def gemm_fp8_blockscaled(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.nd
     _run(_split(m, threads), lambda lo, hi: lib().krn_oracle_gemm_fp8_blockscaled(
         c_type, _p(a), _p(sa), _p(b), _p(sb), _p(c), m, n, k, k, k, n, sa.shape[1], sb.shape[1], lo, hi))
     return c
+
+
+def gemm_mxfp8(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.ndarray, *, c_type: int = BF16, threads: int = 1) -> np.ndarray:
+    """C = sum over 32-wide K blocks of 2^(sa-127) 2^(sb-127) (a8 . b8): a (M, K), b (N, K) e4m3 codes, sa (M, K/32),
+    sb (N, K/32) e8m0 bytes."""
+    a, b = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(b, np.uint8)
+    sa, sb = np.ascontiguousarray(sa, np.uint8), np.ascontiguousarray(sb, np.uint8)
+    (m, k), n = a.shape, b.shape[0]
+    c = np.zeros((m, n), _NUMPY[c_type])
+    _run(_split(m, threads), lambda lo, hi: lib().krn_oracle_gemm_mxfp8(
+        c_type, _p(a), _p(sa), _p(b), _p(sb), _p(c), m, n, k, k, k, n, sa.shape[1], sb.shape[1], lo, hi))
+    return c
+
+
+def quantize_mxfp8(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """e4m3 codes + e8m0 scale bytes, one scale per 1 x 32 block of a row, by the OCP MX rule the reference's format
+    names (`ScaleRounding.FLOOR`, src/krn/data/formats.py:34-37,138-144): scale = 2^(floor(log2 amax) - 8), 8 being the
+    exponent of the largest e4m3 value (448 = 1.75 * 2^8); elements are x / scale rounded to nearest even, saturating.
+    A block of zeros gets the scale 2^0."""
+    rows, cols = x.shape
+    if cols % 32:
+        raise ValueError("the row length must be a multiple of 32")
+    blocks = np.ascontiguousarray(x, np.float32).reshape(rows, cols // 32, 32)
+    amax = np.abs(blocks).max(axis=2)
+    exponent = np.where(amax > 0, np.floor(np.log2(np.where(amax > 0, amax, 1.0))) - 8, 0).astype(np.int32)
+    exponent = np.clip(exponent, -127, 127)
+    scaled = blocks * np.exp2(-exponent.astype(np.float32))[:, :, None]
+    return e4m3_encode(scaled.reshape(rows, cols)), (exponent + 127).astype(np.uint8)
+
+
+def mxfp8_values(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """float64 values of an MXFP8 matrix."""
+    return e4m3_decode(codes).astype(np.float64) * np.repeat(np.exp2(scales.astype(np.float64) - 127), 32, axis=1)
 
 
 def quantize_blocks(x: np.ndarray, block: tuple[int, int]) -> tuple[np.ndarray, np.ndarray]:

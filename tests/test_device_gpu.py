@@ -163,8 +163,8 @@ def test_refusals_happen_before_any_launch(device) -> None:
 def test_plain_function_callers(device) -> None:
     torch = pytest.importorskip("torch")
     a_codes, sa, b_codes, sb = o.config_gemm_fp8(128, 256, 256, seed=2)
-    qa = ops.QMatrix(device.to_device(a_codes, krn.f8e4m3fn), device.to_device(sa), (1, 128))
-    qb = ops.QMatrix(device.to_device(b_codes, krn.f8e4m3fn), device.to_device(sb), (128, 128))
+    qa = ops.QMatrix(krn.formats.FP8FN(), a_codes.shape, device.to_device(a_codes, krn.f8e4m3fn), device.to_device(sa))
+    qb = ops.QMatrix(krn.formats.FP8FNWeights(), b_codes.shape, device.to_device(b_codes, krn.f8e4m3fn), device.to_device(sb))
     out = device.empty(krn.bf16, 128, 256)
     ops.matmul_fp8_blockscaled(qa, qb, out)
     torch.cuda.synchronize()
