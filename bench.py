@@ -6,7 +6,7 @@ Headline workload: the bf16 tile product C = A @ B^T with M = N = K = 8192, f32 
 configuration the headline metric is quoted on. A "step" is one pass of the hot path over one batch of synthetic
 operands (seeded N(0,1), generated on the device). With the default `--workload all` the line also carries
 `workloads`: one sub-record with the same keys for each of the other configurations — `gemm_fp8` (block-scaled e4m3,
-8192 x 28672 x 8192), `attn_fwd` (causal GQA flash attention, B=8, Hq=32, Hkv=8, S=4096, D=128), `attn_decode` (paged
+8192 x 28672 x 8192), `gemm_mxfp8` (the same extents in the MXFP8 format, scales applied by the tensor cores), `attn_fwd` (causal GQA flash attention, B=8, Hq=32, Hkv=8, S=4096, D=128), `attn_decode` (paged
 FP8 decode, 64 sequences, contexts 1024..8192). `--workload NAME` measures that one alone as the headline.
 
 Timing: W (at least 3) warm-up steps, then TRIALS of exactly K steps each, every trial bracketed by a barrier and a
@@ -59,7 +59,7 @@ if str(ROOT) not in sys.path:
 # gemm_bf16 / gemm_fp8 / attn_fwd: captured on a smaller case (see profiles/) and scaled to the full launch by the
 # algorithmic bytes, which DRAM traffic follows for these streaming operand/output patterns; attn_decode: captured on
 # the bench workload itself.
-NCU_TRAFFIC_BYTES = {"gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(220.3e6 * 773.9 / 193.5),
+NCU_TRAFFIC_BYTES = {"gemm_mxfp8": None, "gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(220.3e6 * 773.9 / 193.5),
                      "attn_fwd": int(137.6e6 * 671.1 / 167.8), "attn_decode": int(690.2e6)}
 
 
@@ -380,6 +380,90 @@ class GemmFp8(Workload):
         return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
 
 
+class GemmMxfp8(Workload):
+    """MXFP8 product (e4m3 codes, one e8m0 scale per 1 x 32 block, scales applied by the tensor cores) at the C3 extents
+    M=8192 N=28672 K=8192 (seed 2), bf16 out. One GPU only (no sharded entry point exists for it)."""
+
+    name, metric, dtype = "gemm_mxfp8", "mxfp8_gemm_tflops", "fp8_e4m3"
+    description = "MXFP8 GEMM M=8192 N=28672 K=8192, e8m0 scales per 1x32 block fed to the block-scaled MMA, bf16 out (seed 2)"
+    m, n, k = 8192, 28672, 8192
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        super().__init__(torch, rank, world)
+        if size:
+            self.m, self.n, self.k = size
+            self.description = f"MXFP8 GEMM M={self.m} N={self.n} K={self.k} (profiling case)"
+        if world > 1:
+            raise RuntimeError("the MXFP8 product has no sharded entry point: measured on one GPU only")
+        gen = torch.Generator(device="cuda").manual_seed(2)
+        self.a, self.sa = self._quantize(torch.randn((self.m, self.k), device="cuda", generator=gen))
+        self.b, self.sb = self._quantize(torch.randn((self.n, self.k), device="cuda", generator=gen))
+        self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+
+    def _quantize(self, x):
+        """The OCP MX floor rule on the device: scale 2^(floor(log2 absmax) - 8) per 1 x 32 block, codes e4m3(x / scale)."""
+        torch = self.torch
+        rows, cols = x.shape
+        blocks = x.view(rows, cols // 32, 32)
+        absmax = blocks.abs().amax(dim=2)
+        exponent = torch.where(absmax > 0, torch.floor(torch.log2(torch.where(absmax > 0, absmax, torch.ones_like(absmax)))) - 8,
+                               torch.zeros_like(absmax)).clamp_(-127, 127)
+        codes = (blocks * torch.exp2(-exponent)[:, :, None]).clamp_(-448, 448).reshape(rows, cols).to(torch.float8_e4m3fn)
+        return codes, (exponent + 127).to(torch.uint8).contiguous()
+
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k, "sharding": "one GPU, no exchange",
+                "l2": self.l2_note("operands and output", self.m * self.k + self.n * self.k + 2 * self.m * self.n, 1)}
+
+    def work(self) -> float:
+        return 2.0 * self.m * self.n * self.k
+
+    kernel_work = work
+
+    def peak(self, peaks: dict) -> tuple[float, str]:
+        return 2.0 * peaks["bf16_tflops_sustained"], "2 x sustained cuBLAS bf16 (no FP8 peak was measured on this pool)"
+
+    def step(self, calls) -> None:
+        calls.gemm_mxfp8_tn(self.a, self.sa, self.b, self.sb, self.c, self.torch.cuda.current_stream())
+
+    kernel_only = step
+
+    def host_buffers(self):
+        raise RuntimeError("no host-operand streaming class exists for the MXFP8 product")
+
+    def parity_sample(self, oracle, calls) -> dict:
+        import numpy as np
+
+        torch = self.torch
+        self.step(calls)
+        torch.cuda.synchronize()
+        rows = [0, 1, 127, 128, self.m // 2, self.m - 129, self.m - 128, self.m - 1]
+        host = lambda t: t.contiguous().view(torch.uint8).cpu().numpy()
+        errors = []
+        for lo in (0, (self.n // 2) // 256 * 256, self.n - 256):
+            want = oracle.bf16_values(oracle.gemm_mxfp8(host(self.a[rows]), host(self.sa[rows]), host(self.b[lo:lo + 256]),
+                                                        host(self.sb[lo:lo + 256]), threads=8))
+            got = oracle.bf16_values(self.c[rows, lo:lo + 256].contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+            errors.append(oracle.rel_frobenius(got, want))
+        return {"value": max(errors), "tolerance": 3e-2,
+                "sample": f"{len(rows)} rows x the first, a middle and the last 256-column tile against the oracle"}
+
+    def cpu_sample(self, oracle, cores: int, columns: int | None = None):
+        import numpy as np
+
+        n = columns or 2048
+        rows = 64 * cores
+        rng = np.random.default_rng(2)
+        a_codes, sa = oracle.quantize_mxfp8(rng.standard_normal((rows, self.k), np.float32))
+        b_codes, sb = oracle.quantize_mxfp8(rng.standard_normal((n, self.k), np.float32))
+
+        def run() -> None:
+            oracle.gemm_mxfp8(a_codes, sa, b_codes, sb, threads=cores)
+
+        return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
+
+
 class AttnFwd(Workload):
     """Causal GQA flash attention forward, B=8 Hq=32 Hkv=8 S=4096 D=128, bf16 (seed 3). Sharded by batch."""
 
@@ -594,7 +678,7 @@ class AttnDecode(Workload):
         return self._bytes(tokens, cores), f"{cores} sequences with contexts U[1024,2048], {cores} threads", run
 
 
-WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, AttnFwd, AttnDecode)}
+WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, GemmMxfp8, AttnFwd, AttnDecode)}
 
 
 def cpu_rates(workload, oracle, cores: int, columns: int | None, repeats: int = 1) -> dict:
@@ -808,7 +892,7 @@ def main() -> int:
 
     others = {}
     if args.workload == "all" and not args.size:
-        for name in ("gemm_fp8", "attn_fwd", "attn_decode"):
+        for name in ("gemm_fp8", "gemm_mxfp8", "attn_fwd", "attn_decode") if world == 1 else ("gemm_fp8", "attn_fwd", "attn_decode"):
             try:
                 workload = WORKLOADS[name](torch, rank, world, None)
                 # with N > 1 the sub-records carry the device-resident numbers only (the run stays within minutes)
