@@ -320,7 +320,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-    if (lane == 0) tma_store_wait<0>();
+    if (lane == 0) {
+      tma_store_wait<0>();
+      // When the stores went to other ranks, the thread that issued them orders them system-wide itself, before the
+      // CTA barrier that precedes the cross-rank flag (completion of a bulk group is a statement about this thread's
+      // view of its own copies; the flag is written by another thread).
+      if (sync.ranks > 1) {
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence_system();
+      }
+    }
   }
 
   // ------------------------------------------------------------------ teardown
