@@ -259,18 +259,42 @@ def _attention(kernel: ir.Kernel) -> AttentionPlan | None:
     if kinds != ["maximum", "exp2:sub", "exp2:sub", "mul", "add", "mul", "accumulate", "copy"]:
         return None
     m_new, p, corr, total_scale, total_add, acc_scale, _, m_copy = body
-    if not (isinstance(m_new.value.operands[1], ir.Reduce) and m_new.value.operands[1].op == "max"
-            and isinstance(total_add.value.operands[1], ir.Reduce) and total_add.value.operands[1].op == "sum"
-            and total_add.value.operands[1].operand == p.var and pv.lhs.operand == p.var
-            and total_scale.value.operands[1] == corr.var and acc_scale.value.operands[1] == corr.var
-            and acc_scale.var == pv.acc and m_copy.value == m_new.var):
+    s_var, m_var = score.var, m_copy.var  # the scores and the running maximum (`m = m_new` names it)
+    l_var, acc_var = total_add.var, pv.acc
+
+    def is_sub(e, lhs, rhs) -> bool:
+        return isinstance(e, ir.Math) and e.fn == "sub" and e.operands == (lhs, rhs)
+
+    row_max, row_sum = m_new.value.operands[1], total_add.value.operands[1]
+    checks = (
+        # m_new = maximum(m, max(s, axis=1)): the running maximum first, the row maximum of THE SCORES second
+        m_new.value.operands[0] == m_var,
+        isinstance(row_max, ir.Reduce) and row_max.op == "max" and row_max.operand == s_var and row_max.axis == 1,
+        # p = exp2(s - m_new), corr = exp2(m - m_new): against the NEW maximum, from the OLD one
+        is_sub(p.value.operands[0], s_var, m_new.var),
+        is_sub(corr.value.operands[0], m_var, m_new.var),
+        # l = l * corr + sum(p, axis=1); acc = acc * corr + p.to(T) @ v; m = m_new
+        total_scale.var == l_var and total_scale.value.operands == (l_var, corr.var),
+        total_add.value.operands[0] == l_var,
+        isinstance(row_sum, ir.Reduce) and row_sum.op == "sum" and row_sum.operand == p.var and row_sum.axis == 1,
+        acc_scale.var == acc_var and acc_scale.value.operands == (acc_var, corr.var),
+        pv.lhs.operand == p.var,
+        m_copy.value == m_new.var,
+        # both sums start from zero
+        isinstance(assigns.get(l_var.name), ir.Zeros) and assigns[l_var.name].value == 0.0,
+        isinstance(assigns.get(acc_var.name), ir.Zeros) and assigns[acc_var.name].value == 0.0,
+    )
+    if not all(checks):
         return None
+    if causal and select.value.then != s_var:
+        return None  # the mask keeps something other than the score itself
     final = store.value
     if not (isinstance(final, ir.Cast) and isinstance(final.operand, ir.Math) and final.operand.fn == "div"
             and final.operand.operands[0] == pv.acc and final.operand.operands[1] == total_add.var):
         return None
-    start = assigns.get(m_copy.var.name)
-    if not (isinstance(start, ir.Math) and start.fn == "sub" and isinstance(start.operands[0], ir.Zeros)):
+    start = assigns.get(m_copy.var.name)  # the running maximum starts at 0 - 1e30 (or lower)
+    if not (isinstance(start, ir.Math) and start.fn == "sub" and isinstance(start.operands[0], ir.Zeros)
+            and start.operands[0].value == 0.0 and isinstance(start.operands[1], ir.Const) and start.operands[1].value >= 1.0e29):
         return None
     dtype = qt.dtype
     if dtype.name not in ("bf16", "f16") or any(t.dtype != dtype for t in (kt, vt)) or pv.lhs.dtype != dtype:

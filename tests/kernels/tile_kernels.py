@@ -1,7 +1,7 @@
 """Kernel sources the front-end tests capture (capture reads source files, so kernels live in a module)."""
 
 from krn_b200 import (Const, Feature, Matrix, PingPong, Space, T, Tensor, Vector, WarpSpecialized, arange, bf16, block, f16,
-                      f32, family, kernel, pipelined, struct, targets, where, zeros)
+                      f32, family, full, kernel, pipelined, struct, targets, where, zeros)
 
 
 @struct
@@ -102,6 +102,64 @@ def flash_attention(t: Heads, q: Tensor[T.f16, int, int, int], k: Tensor[T.f16, 
             s = where(arange(t.bk, 1, rank=2, start=c) <= q_pos, s, -1.0e30)
         m_new = m.maximum(s.max(keepdims=True))
         p, corr = (s - m_new).exp2(), (m - m_new).exp2()
+        total *= corr
+        total += p.sum(keepdims=True)
+        acc *= corr
+        acc += p.to(T.f16) @ v[head, c : c + t.bk, slice(0, t.d)]
+        m = m_new
+    o[head, rows, slice(0, t.d)] = (acc / total).to(T.f16)
+
+
+# ---- near misses of the attention pattern: each differs from the example in ONE operand and must be refused, not run
+# as standard attention
+
+
+@kernel
+def attention_old_maximum_in_exponent(t: Heads, q: Tensor[T.f16, int, int, int], k: Tensor[T.f16, int, int, int],
+                                      v: Tensor[T.f16, int, int, int], o: Tensor[T.f16, int, int, int], scale: T.f32) -> None:
+    rows, head = block.tile(t.bq), block.index().y
+    m, total, acc = zeros(T.f32, t.bq, 1).sub(1.0e30), zeros(T.f32, t.bq, 1), zeros(T.f32, t.bq, t.d)
+    qt = q[head, rows, slice(0, t.d)]
+    for c in range(0, k.shape[1], t.bk):
+        s = (qt @ k[head, c : c + t.bk, slice(0, t.d)].transpose()).mul(scale)
+        m_new = m.maximum(s.max(keepdims=True))
+        p, corr = (s - m).exp2(), (m - m_new).exp2()  # exponent against the OLD maximum
+        total *= corr
+        total += p.sum(keepdims=True)
+        acc *= corr
+        acc += p.to(T.f16) @ v[head, c : c + t.bk, slice(0, t.d)]
+        m = m_new
+    o[head, rows, slice(0, t.d)] = (acc / total).to(T.f16)
+
+
+@kernel
+def attention_sum_starts_at_one(t: Heads, q: Tensor[T.f16, int, int, int], k: Tensor[T.f16, int, int, int],
+                                v: Tensor[T.f16, int, int, int], o: Tensor[T.f16, int, int, int], scale: T.f32) -> None:
+    rows, head = block.tile(t.bq), block.index().y
+    m, total, acc = zeros(T.f32, t.bq, 1).sub(1.0e30), full(T.f32, 1.0, t.bq, 1), zeros(T.f32, t.bq, t.d)
+    qt = q[head, rows, slice(0, t.d)]
+    for c in range(0, k.shape[1], t.bk):
+        s = (qt @ k[head, c : c + t.bk, slice(0, t.d)].transpose()).mul(scale)
+        m_new = m.maximum(s.max(keepdims=True))
+        p, corr = (s - m_new).exp2(), (m - m_new).exp2()
+        total *= corr
+        total += p.sum(keepdims=True)
+        acc *= corr
+        acc += p.to(T.f16) @ v[head, c : c + t.bk, slice(0, t.d)]
+        m = m_new
+    o[head, rows, slice(0, t.d)] = (acc / total).to(T.f16)
+
+
+@kernel
+def attention_correction_swapped(t: Heads, q: Tensor[T.f16, int, int, int], k: Tensor[T.f16, int, int, int],
+                                 v: Tensor[T.f16, int, int, int], o: Tensor[T.f16, int, int, int], scale: T.f32) -> None:
+    rows, head = block.tile(t.bq), block.index().y
+    m, total, acc = zeros(T.f32, t.bq, 1).sub(1.0e30), zeros(T.f32, t.bq, 1), zeros(T.f32, t.bq, t.d)
+    qt = q[head, rows, slice(0, t.d)]
+    for c in range(0, k.shape[1], t.bk):
+        s = (qt @ k[head, c : c + t.bk, slice(0, t.d)].transpose()).mul(scale)
+        m_new = m.maximum(s.max(keepdims=True))
+        p, corr = (s - m_new).exp2(), (m_new - m).exp2()  # the correction's operands swapped
         total *= corr
         total += p.sum(keepdims=True)
         acc *= corr

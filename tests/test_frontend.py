@@ -76,6 +76,16 @@ def test_recognise_fp8_pairs() -> None:
     assert plan.transposed_b and (plan.operand.name, plan.operand_b.name, plan.output.name) == ("f8e4m3fn", "f8e4m3fn", "bf16")
 
 
+@pytest.mark.parametrize("near_miss", ["attention_old_maximum_in_exponent", "attention_sum_starts_at_one",
+                                       "attention_correction_swapped"])
+def test_near_misses_of_the_attention_pattern_are_refused(near_miss) -> None:
+    """A body that differs from the example's online softmax in one operand is not standard attention: it must be refused
+    with the four-part message, never run as the prebuilt kernel ("never ignore it silently")."""
+    with pytest.raises(TargetError) as error:
+        recognise(capture(getattr(K, near_miss).fn, K.Heads()))
+    assert "is not available on sm_100a" in str(error.value) and "Instead:" in str(error.value)
+
+
 def test_recognise_library_epilogues() -> None:
     """The reference's `matmul_epilogue` kernel (src/krn/lib/lib_kernels.py:30-48) under each flag set."""
     tile = (64, 64, 32)
