@@ -6,14 +6,21 @@
 // block-scaled MMA" in the literal sense — so nothing is dequantised and no partial sum leaves tensor memory before the
 // last K block.
 //
-// Roles per CTA (256 threads, one 128 x 256 output tile at a time, persistent over tiles):
-//   warp 0      TMA producer: A (128 rows) and B (256 rows) tiles of 128 codes per row into a 4-stage ring
+// Tiles: a CTA pair on a 256 x 256 tile (cta_group::2: each CTA holds 128 rows of A, 128 of the 256 rows of B, and its
+// own 128 x 256 half of the accumulator) whenever M > 128, else one CTA on a 128 x 256 tile. The pair moves 32 KB per K
+// block and CTA through L2 and shared memory instead of 48 KB, which is what the single-CTA form is limited by.
+//
+// Roles per CTA (256 threads, persistent over tiles):
+//   warp 0      TMA producer: A and B tiles of 128 codes per row into a ring of stages of TWO K blocks each (3 x 64 KB
+//               paired, 2 x 96 KB alone): one barrier per 256 codes of K halves the issuing thread's polls and commits
 //   warp 1      MMA issuer: per K block of 128 codes, copies that block's scale factors from shared memory into tensor
 //               memory (tcgen05.cp, 32x128b.warpx4: one 512-byte group per 128 rows) and issues four K = 32
 //               instructions whose descriptors select the scale byte of their 32-wide sub-block
-//   warps 2-3   scale loaders: fetch, four K blocks at a time, the 16 scale bytes of every row of the tile (one 16-byte
-//               load per row) and lay them out in shared memory the way tcgen05.cp expects a 128-row group:
-//               byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block
+//   warps 2-3   scale loaders: fetch, four K blocks at a time, the 16 scale bytes of this CTA's 128 A rows and of ALL 256
+//               B rows of the tile (each CTA of a pair multiplies its A rows by every column, so it needs every column's
+//               scale) and lay them out in shared memory the way tcgen05.cp expects a 128-row group:
+//               byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block. In a pair the leader's one tcgen05.cp
+//               (cta_group::2) makes each CTA copy from its OWN shared memory into its own tensor memory
 //   warps 4-7   epilogue: tensor memory -> registers -> output type -> swizzled staging -> TMA store
 //
 // Tensor memory (512 columns): 256 accumulator columns, then 4 columns of A scales and 8 of B scales. One accumulator
@@ -31,19 +38,26 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 128;          // codes per stage row = four 32-wide scale blocks
 constexpr int kThreads = 256;
-constexpr int kStages = 4;
 constexpr int kABytes = kBM * 128;
-constexpr int kBBytes = kBN * 128;
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kScaleChunk = 4;                          // K blocks of scales per ring slot (16 scale bytes per row)
 constexpr int kScaleBlockBytes = 512 + 2 * 512;         // one K block: the A group, then two B groups of 128 rows
-constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-constexpr int kEpilogueBytes = 4 * 4096;                // per epilogue warp: one 32-row x 128-byte store box
-constexpr int kSmemBytes = kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
+constexpr int kEpilogueBytes = 4 * 2048;                // per epilogue warp: one 16-row x 128-byte store box
+template <int CTA_GROUP>
+struct Layout {
+  static constexpr int kBRows = kBN / CTA_GROUP;           // rows of B this CTA loads
+  static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block of 128 codes: this CTA's A and B rows
+  static constexpr int kStageBytes = 2 * kBlockBytes;         // a stage = two K blocks behind ONE barrier
+  // K blocks of scales per ring slot. A pair takes eight (32 scale bytes per row): the peer's loaders signal the leader
+  // with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide that
+  // together with the global-memory latency behind the K blocks of the other slot; four were measured 17 % slower.
+  static constexpr int kScaleChunk = CTA_GROUP == 2 ? 8 : 4;
+  static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
+  static constexpr int kStages = CTA_GROUP == 2 ? 3 : 2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
+};
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // column of the A scale factors (4 columns)
 constexpr int kTmemScaleB = 260;                        // column of the B scale factors (8 columns)
-static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(Layout<1>::kSmemBytes <= 232448 && Layout<2>::kSmemBytes <= 232448, "shared memory budget");
 
 struct MxScales {
   const uint8_t* sa;  // [M, K / 32] e8m0
@@ -55,40 +69,61 @@ struct MxScales {
 enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
             kSiteScaleEmpty = 46 };
 
+
 // Instruction descriptor of kind::mxf8f6f4.block_scale: B scale id [4,6), A format [7,10), B format [10,13), majors 15 /
 // 16, N / 8 at [17,23), scale format (1 = e8m0) at 23, M / 16 at [24,29), A scale id [29,31). The scale id picks which
 // of the four bytes of a scale-factor column belongs to this instruction's 32-wide K sub-block.
-__device__ __forceinline__ uint32_t mx_idesc(uint32_t sub_block) {
+__device__ __forceinline__ uint32_t mx_idesc(uint32_t sub_block, uint32_t m) {
   return (sub_block << 4) | (kFmtE4M3 << 7) | (kFmtE4M3 << 10) | (uint32_t(kBN >> 3) << 17) | (1u << 23) |
-         (uint32_t(kBM >> 4) << 24) | (sub_block << 29);
+         ((m >> 4) << 24) | (sub_block << 29);
 }
 
 // D[tmem] (+)= (A * scale_a) * (B * scale_b): A, B shared-memory descriptors, scales in tensor memory. One thread.
+template <int CTA_GROUP>
 __device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
                                         uint32_t scale_a_tmem, uint32_t scale_b_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
-      " tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%5], [%6], p;\n}\n"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
-      : "memory");
+  if constexpr (CTA_GROUP == 1) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  }
 }
 
 // 512 bytes of shared memory (32 rows of 16 bytes, unswizzled: 8-row groups 128 bytes apart) -> 4 tensor-memory columns,
 // the same 32 x 16 bytes into each of the four 32-lane quarters.
+template <int CTA_GROUP>
 __device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t smem_addr) {
   uint64_t desc = 0;
   desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
   desc |= static_cast<uint64_t>(128 >> 4) << 32;               // stride between 8-row groups
   desc |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_column), "l"(desc) : "memory");
+  if constexpr (CTA_GROUP == 1) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_column), "l"(desc) : "memory");
+  } else {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_column), "l"(desc) : "memory");
+  }
 }
 
-template <typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, Problem p, MxScales scales, DeviceStatus* status) {
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
+  using L = Layout<CTA_GROUP>;
+  constexpr int kStages = L::kStages;
+  constexpr int kStageBytes = L::kStageBytes;
+  constexpr int kBlockBytes = L::kBlockBytes;
+  constexpr int kScaleChunk = L::kScaleChunk;
+  constexpr int kScaleSlotBytes = L::kScaleSlotBytes;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -110,6 +145,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
+  const uint32_t rank = CTA_GROUP == 2 ? cluster_ctarank() : 0u;
+  const int first_tile = blockIdx.x / CTA_GROUP;   // this cluster's first tile
+  const int tile_step = gridDim.x / CTA_GROUP;     // clusters in the grid
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = p.k / kBK;
 
@@ -119,11 +157,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(scale_full_bar + 8 * s, 2);   // the two loader warps
-      mbar_init(scale_empty_bar + 8 * s, 1);  // the issuing thread's commit
+      mbar_init(scale_full_bar + 8 * s, 2 * CTA_GROUP);  // the two loader warps of every CTA of the tile
+      mbar_init(scale_empty_bar + 8 * s, 1);             // the issuing thread's commit
     }
     mbar_init(tmem_full_bar, 1);
-    mbar_init(tmem_empty_bar, 4);
+    mbar_init(tmem_empty_bar, 4 * CTA_GROUP);            // the epilogue warps of every CTA of the tile
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_a);
@@ -131,11 +169,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     prefetch_tensormap(&map_c);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(tmem_slot), kTmemColumns);
-    tmem_relinquish<1>();
+    tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
+    tmem_relinquish<CTA_GROUP>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -145,18 +187,33 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
         tile_coords(t, p, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int row_a = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
+        const int row_b = tn * kBN + int(rank) * L::kBRows;
+        for (int kb = 0; kb < num_kb; kb += 2) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
             ok = false;
             break;
           }
-          const uint32_t a_dst = stages_addr + stage * kStageBytes;
-          mbar_arrive_expect_tx(full_bar + 8 * stage, kStageBytes);
-          tma_load_2d(a_dst, &map_a, kb * kBK, tm * kBM, full_bar + 8 * stage);
-          tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, tn * kBN, full_bar + 8 * stage);
+          const int blocks = min(2, num_kb - kb);  // an odd K-block count leaves the last stage half full
+          const uint32_t dst = stages_addr + stage * kStageBytes;
+          if constexpr (CTA_GROUP == 1) {
+            mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * kBlockBytes);
+            for (int j = 0; j < blocks; ++j) {
+              tma_load_2d(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, full_bar + 8 * stage);
+              tma_load_2d(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, full_bar + 8 * stage);
+            }
+          } else {
+            // both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both
+            if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * 2u * kBlockBytes);
+            const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+            for (int j = 0; j < blocks; ++j) {
+              tma_load_2d_pair(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, leader_full);
+              tma_load_2d_pair(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, leader_full);
+            }
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -165,66 +222,88 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
       const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
       const uint32_t desc_hi = uint32_t(desc0 >> 32);
-      uint32_t a_lo = uint32_t(desc0);
       int stage = 0;
       uint32_t phase = 0, chunk = 0, iter = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+      // This thread is the kernel's critical path: every tcgen05 instruction it issues costs about 60 cycles and a
+      // barrier poll about 220 even when it succeeds at once (cycle trace with one K block per barrier: 851 cycles per K
+      // block — poll 241, three scale copies 164, four products 257, commit 119 — against 512 of tensor work). Hence
+      // two K blocks per barrier: one poll and one commit per 256 codes of K.
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++iter) {
         // the single accumulator must have been read out by the epilogue of the previous tile
         if (!mbar_wait(tmem_empty_bar, (iter & 1u) ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const uint32_t slot = chunk & 1u;
-          const int in_chunk = kb & (kScaleChunk - 1);
-          if (in_chunk == 0 &&
-              !mbar_wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, abort_flag, status, kSiteMmaScale)) {
-            ok = false;
-            break;
-          }
+        for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
-          scales_to_tmem(tmem_base + kTmemScaleA, block);
-          scales_to_tmem(tmem_base + kTmemScaleB, block + 512);
-          scales_to_tmem(tmem_base + kTmemScaleB + 4, block + 1024);
-          const uint32_t b_lo = a_lo + (kABytes >> 4);
+          const int blocks = min(2, num_kb - kb0);
+          for (int j = 0; j < blocks && ok; ++j) {
+            const int kb = kb0 + j;
+            const uint32_t slot = chunk & 1u;
+            const int in_chunk = kb & (kScaleChunk - 1);
+            if (in_chunk == 0) {
+              if (!mbar_wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, abort_flag, status, kSiteMmaScale)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
+            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
+            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
+            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
+            const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
+            const uint32_t b_lo = a_lo + (kABytes >> 4);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            umma_mx(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks), tmem_base + kTmemScaleA,
-                    tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
+                                 tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
+            }
+            if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) {
+              if constexpr (CTA_GROUP == 1) {
+                umma_commit(scale_empty_bar + 8 * slot);
+              } else {
+                umma_commit_pair(scale_empty_bar + 8 * slot, 0x3);
+              }
+              ++chunk;
+            }
           }
-          umma_commit(empty_bar + 8 * stage);
-          if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) {
-            umma_commit(scale_empty_bar + 8 * slot);
-            ++chunk;
+          if (!ok) break;
+          if constexpr (CTA_GROUP == 1) {
+            umma_commit(empty_bar + 8 * stage);
+          } else {
+            umma_commit_pair(empty_bar + 8 * stage, 0x3);
           }
-          a_lo += kStageBytes >> 4;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
-            a_lo = uint32_t(desc0);
           }
         }
         if (!ok) break;
-        umma_commit(tmem_full_bar);
+        if constexpr (CTA_GROUP == 1) {
+          umma_commit(tmem_full_bar);
+        } else {
+          umma_commit_pair(tmem_full_bar, 0x3);
+        }
       }
     }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- scale loaders (64 threads)
-    // Per ring slot: the 16 scale bytes (four K blocks) of the tile's 128 A rows and 256 B rows — 384 rows, six per
-    // thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
+    // Per ring slot: the 16 scale bytes (four K blocks) of this CTA's 128 A rows and the tile's 256 B rows — 384 rows,
+    // six per thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
     // group. Rows beyond the matrix get the code of 2^0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
     uint32_t chunk = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       int tm, tn;
       tile_coords(t, p, tm, tn);
       for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk) {
@@ -241,14 +320,20 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
           const bool is_a = r < kBM;
           const int local = is_a ? r : r - kBM;
-          const long long row = is_a ? (long long)tm * kBM + local : (long long)tn * kBN + local;
+          const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
+                                     : (long long)tn * kBN + local;
           const bool live = row < (is_a ? p.m : p.n);
-          uint32_t w[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+          uint32_t w[kScaleChunk];
+#pragma unroll
+          for (int j = 0; j < kScaleChunk; ++j) w[j] = 0x7f7f7f7fu;
           if (live) {
             const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 4;
             if (blocks_here == kScaleChunk && scales.vector_ok) {
-              const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
-              w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+#pragma unroll
+              for (int q = 0; q < kScaleChunk / 4; ++q) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + q);
+                w[4 * q] = v.x, w[4 * q + 1] = v.y, w[4 * q + 2] = v.z, w[4 * q + 3] = v.w;
+              }
             } else {
               for (int j = 0; j < blocks_here; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
             }
@@ -261,19 +346,26 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
         __syncwarp();
-        if (lane == 0) mbar_arrive(scale_full_bar + 8 * slot);
+        if (lane == 0) {
+          if constexpr (CTA_GROUP == 2) {
+            mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
+          } else {
+            mbar_arrive(scale_full_bar + 8 * slot);
+          }
+        }
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue warps
     const int quarter = warp & 3;  // the 32-lane slice of tensor memory this warp may read
-    const uint32_t buffer = epilogue_addr + quarter * 4096;
+    const uint32_t buffer = epilogue_addr + quarter * 2048;
+    const uint32_t leader_tmem_empty = CTA_GROUP == 2 ? map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
     uint32_t iter = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++iter) {
       int tm, tn;
       tile_coords(t, p, tm, tn);
-      const int row0 = tm * kBM + quarter * 32;
+      const int row0 = tm * (kBM * CTA_GROUP) + int(rank) * kBM + quarter * 32;
       const int col0 = tn * kBN;
       if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar, iter & 1u, abort_flag, status, kSiteEpilogueFull))) {
         ok = false;
@@ -281,15 +373,63 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kChunks; ++chunk) {
+      auto store_chunk = [&](int chunk, const uint32_t (&words)[32]) {
+        // the warp's 32 rows x 128 bytes go out as two 16-row boxes through its 2 KB staging buffer (swizzled as the
+        // tensor map expects); shared memory is spent on operand stages instead of a larger buffer
         const int col = col0 + chunk * kChunkCols;
-        const bool live = row0 < p.m && col < p.n;  // warp-uniform
-        uint32_t packed[32];
-        if constexpr (sizeof(OutT) == 4) {
-          tmem_ld_32x32(t_row + chunk * kChunkCols, packed);
-          tmem_ld_wait(packed);
-        } else {
+        if (row0 < p.m && col < p.n) {  // warp-uniform
+#pragma unroll
+          for (int rows_half = 0; rows_half < 2; ++rows_half) {
+            if (lane == 0) tma_store_wait_read<0>();  // the previous store has read this buffer
+            __syncwarp();
+            if (int(lane >> 4) == rows_half) {
+              const uint32_t row_addr = buffer + (lane & 15u) * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(words[4 * j]),
+                             "r"(words[4 * j + 1]), "r"(words[4 * j + 2]), "r"(words[4 * j + 3])
+                             : "memory");
+              }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (row0 + rows_half * 16 < p.m) tma_store_2d(&map_c, col, row0 + rows_half * 16, buffer);
+              tma_store_commit();
+            }
+          }
+        }
+      };
+      auto hand_back = [&]() {
+        // the accumulator has been read completely: the next tile's products may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTA_GROUP == 2) {
+            mbar_arrive_cluster(leader_tmem_empty);
+          } else {
+            mbar_arrive(tmem_empty_bar);
+          }
+        }
+      };
+      if constexpr (sizeof(OutT) == 4) {
+        // f32 output: 256 values per thread do not fit the register file, so the stores sit between the reads
+#pragma unroll 1
+        for (int chunk = 0; chunk < kChunks; ++chunk) {
+          uint32_t words[32];
+          tmem_ld_32x32(t_row + chunk * kChunkCols, words);
+          tmem_ld_wait(words);
+          if (chunk == kChunks - 1) hand_back();
+          store_chunk(chunk, words);
+        }
+      } else {
+        // 16-bit output: the whole row (256 values) is rounded into 128 registers first, so tensor memory goes back to
+        // the tensor cores after four reads, before any store is waited for (with the stores in between, the reads of
+        // a tile took as long as the store pipeline: a fifth of the tile's time)
+        uint32_t packed[kChunks][32];
+#pragma unroll
+        for (int chunk = 0; chunk < kChunks; ++chunk) {
           uint32_t lo[32], hi[32];
           tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
@@ -297,38 +437,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             if constexpr (OUT_BF16) {
-              packed[i] = pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
-              packed[16 + i] = pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+              packed[chunk][i] = pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[chunk][16 + i] = pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
             } else {
-              packed[i] = pack_f16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
-              packed[16 + i] = pack_f16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+              packed[chunk][i] = pack_f16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+              packed[chunk][16 + i] = pack_f16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
             }
           }
         }
-        if (chunk == kChunks - 1) {
-          // the accumulator has been read completely: hand it back before the last stores
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tmem_empty_bar);
-        }
-        if (live) {
-          if (lane == 0) tma_store_wait_read<0>();  // the previous store has read this buffer
-          __syncwarp();
-          const uint32_t row_addr = buffer + lane * 128;
+        hand_back();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t dst = row_addr + ((uint32_t(j) ^ (lane & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
-                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
-                         : "memory");
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&map_c, col, row0, buffer);
-            tma_store_commit();
-          }
-        }
+        for (int chunk = 0; chunk < kChunks; ++chunk) store_chunk(chunk, packed[chunk]);
       }
     }
     if (lane == 0) tma_store_wait<0>();
@@ -341,22 +460,47 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, kTmemColumns);
+    tmem_dealloc<CTA_GROUP>(tmem_base, kTmemColumns);
   }
 }
 
-template <typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
            MxScales scales, cudaStream_t stream) {
-  auto kernel = gemm_mxfp8_kernel<OutT, OUT_BF16>;
-  KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  using L = Layout<CTA_GROUP>;
+  auto kernel = gemm_mxfp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
+  KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p, scales, ctx->status_dev);
-  KRNB_CUDA(cudaGetLastError());
+  int clusters = ctx->sm_count / CTA_GROUP;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(clusters * CTA_GROUP), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = L::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA_GROUP;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, scales, ctx->status_dev));
   return KRN_B200_OK;
+}
+
+template <int CTA_GROUP>
+int launch_for_output(const DeviceContext* ctx, int c_type, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                      Problem p, MxScales scales, cudaStream_t stream) {
+  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, float, false>(ctx, ma, mb, mc, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
+  return launch<CTA_GROUP, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
 }
 
 }  // namespace
@@ -398,11 +542,12 @@ extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* 
   if (ctx == nullptr) return KRN_B200_ERR_CUDA;
   if (int rc = require_sm100(ctx)) return rc;
 
+  const int group = m > kBM ? 2 : 1;  // a single 128-row panel has nothing for a second CTA to do
   Problem p;
   p.m = int(m);
   p.n = int(n);
   p.k = int(k);
-  p.tiles_m = int((m + kBM - 1) / kBM);
+  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
   p.b_kn = 0;
   MxScales scales = {sa, sb, ldsa, ldsb, (aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0) ? 1 : 0};
@@ -417,7 +562,7 @@ extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* 
   {
     uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
     uint64_t strides[1] = {uint64_t(ldb)};
-    uint32_t box[2] = {128, uint32_t(kBN)};
+    uint32_t box[2] = {128, uint32_t(kBN / group)};
     if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
   }
   {
@@ -426,10 +571,9 @@ extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* 
                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
     uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
-    uint32_t box[2] = {uint32_t(128 / c_bytes), 32};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  if (c_type == KRN_B200_F32) return launch<float, false>(ctx, map_a, map_b, map_c, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<uint16_t, true>(ctx, map_a, map_b, map_c, p, scales, stream);
-  return launch<uint16_t, false>(ctx, map_a, map_b, map_c, p, scales, stream);
+  if (group == 2) return launch_for_output<2>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  return launch_for_output<1>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
 }
