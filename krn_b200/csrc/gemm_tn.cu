@@ -37,8 +37,12 @@ struct Layout {
   static constexpr int kBRows = kBN / CTA_GROUP;
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = kBRows * kRowBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = CTA_GROUP == 2 ? 6 : 4;
+  static constexpr int kBlockStageBytes = kABytes + kBBytes;   // one K block (128 bytes of K per row) of A and B
+  // A stage is TWO K blocks behind one barrier pair. The issuing thread is the kernel's critical path — a barrier poll
+  // costs it about 220 cycles even when it succeeds at once, a commit 60-120, each product about 60 — and one poll and
+  // one commit per K block left it at 520-580 cycles per 512 cycles of tensor work.
+  static constexpr int kStageBytes = 2 * kBlockStageBytes;
+  static constexpr int kStages = CTA_GROUP == 2 ? 3 : 2;
   static constexpr int kEpilogueBytes = 4 * 2 * 4096;  // 4 warps x 2 buffers x (32 rows x 128 bytes)
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + kBarrierBytes + 1024;
@@ -138,33 +142,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tile_coords(t, p, tm, tn);
         const int row_a = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
         const int row_b = tn * kBN + int(rank) * L::kBRows;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
             ok = false;
             break;
           }
-          const uint32_t a_dst = stages_addr + stage * L::kStageBytes;
-          const uint32_t b_dst = a_dst + L::kABytes;
-          if constexpr (CTA_GROUP == 1) {
-            mbar_arrive_expect_tx(full_bar + 8 * stage, L::kStageBytes);
-            tma_load_2d(a_dst, &map_a, kb * kBK, row_a, full_bar + 8 * stage);
-            if (!p.b_kn) {
-              tma_load_2d(b_dst, &map_b, kb * kBK, row_b, full_bar + 8 * stage);
+          const int blocks = min(2, num_kb - kb0);  // an odd number of K blocks leaves the last stage half full
+          const uint32_t leader_full = CTA_GROUP == 2 ? map_to_cta(full_bar + 8 * stage, 0) : full_bar + 8 * stage;
+          // in a pair both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both
+          if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks * CTA_GROUP) * L::kBlockStageBytes);
+          for (int j = 0; j < blocks; ++j) {
+            const int kb = kb0 + j;
+            const uint32_t a_dst = stages_addr + stage * L::kStageBytes + j * L::kBlockStageBytes;
+            const uint32_t b_dst = a_dst + L::kABytes;
+            if constexpr (CTA_GROUP == 1) {
+              tma_load_2d(a_dst, &map_a, kb * kBK, row_a, leader_full);
+              if (!p.b_kn) {
+                tma_load_2d(b_dst, &map_b, kb * kBK, row_b, leader_full);
+              } else {
+                // b is (K, N): boxes of 128 bytes of N x kBK rows of K, N contiguous; one box per kBlockCols columns
+                for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
+                  tma_load_2d(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, leader_full);
+              }
             } else {
-              // b is (K, N): boxes of 128 bytes of N x kBK rows of K, N contiguous; one box per kBlockCols columns
-              for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
-                tma_load_2d(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, full_bar + 8 * stage);
-            }
-          } else {
-            // Both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both.
-            if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * L::kStageBytes);
-            const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
-            tma_load_2d_pair(a_dst, &map_a, kb * kBK, row_a, leader_full);
-            if (!p.b_kn) {
-              tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
-            } else {
-              for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
-                tma_load_2d_pair(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, leader_full);
+              tma_load_2d_pair(a_dst, &map_a, kb * kBK, row_a, leader_full);
+              if (!p.b_kn) {
+                tma_load_2d_pair(b_dst, &map_b, kb * kBK, row_b, leader_full);
+              } else {
+                for (int blk = 0; blk < L::kBRows / kBlockCols; ++blk)
+                  tma_load_2d_pair(b_dst + blk * kBlockBytes, &map_b, row_b + blk * kBlockCols, kb * kBK, leader_full);
+              }
             }
           }
           if (++stage == L::kStages) {
@@ -198,16 +205,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          const int blocks = min(2, num_kb - kb0);
+          for (int j = 0; j < blocks; ++j) {
+            const uint32_t step = uint32_t(j) * (L::kBlockStageBytes >> 4);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            umma_ss_halves<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_lo + 2 * ks, a_hi, b_lo + b_step * ks, b_hi, idesc,
-                                                       (kb > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_ss_halves<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_lo + step + 2 * ks, a_hi, b_lo + step + b_step * ks, b_hi,
+                                                         idesc, (kb0 + j > 0 || ks > 0) ? 1u : 0u);
+            }
           }
           if constexpr (CTA_GROUP == 1) {
             umma_commit(empty_bar + 8 * stage);
