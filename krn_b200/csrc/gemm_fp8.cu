@@ -214,12 +214,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, desc_hi, b_lo + 2 * ks, desc_hi, idesc,
                                             ks > 0 ? 1u : 0u);
           }
+          // the promotion warps wait for the first of these: it is on the kernel's critical cycle (a commit costs the
+          // issuing thread 60-120 cycles), the producer's is not
           if constexpr (CTA_GROUP == 1) {
-            umma_commit(empty_bar + 8 * stage);
             umma_commit(part_full_bar + 8 * buf);
+            umma_commit(empty_bar + 8 * stage);
           } else {
-            umma_commit_pair(empty_bar + 8 * stage, 0x3);
             umma_commit_pair(part_full_bar + 8 * buf, 0x3);
+            umma_commit_pair(empty_bar + 8 * stage, 0x3);
           }
           buf ^= 1u;
           a_lo += L::kStageBytes >> 4;

@@ -3,8 +3,8 @@
 //
 // One persistent, warp-specialised kernel per CTA-pair mode:
 //   warp 0      TMA producer: one lane streams 128-byte-swizzled A and B tiles into a ring of shared-memory
-//               stages and arms the stage's "full" mbarrier with the byte count;
-//   warp 1      MMA issuer: one lane waits for "full", issues four tcgen05.mma (K = 16 each) per stage
+//               stages (two K blocks of 128 bytes per row each) and arms the stage's "full" mbarrier with the byte count;
+//   warp 1      MMA issuer: one lane waits for "full", issues eight tcgen05.mma (32 bytes of K each) per stage
 //               into one of two tensor-memory accumulators and commits the stage's "empty" barrier;
 //   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns 32 lanes = 32 rows), round
 //               to the output type, stage 32x(128 byte) boxes in swizzled shared memory and TMA-store them,
