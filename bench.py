@@ -59,7 +59,7 @@ if str(ROOT) not in sys.path:
 # gemm_bf16 / gemm_fp8 / attn_fwd: captured on a smaller case (see profiles/) and scaled to the full launch by the
 # algorithmic bytes, which DRAM traffic follows for these streaming operand/output patterns; attn_decode: captured on
 # the bench workload itself.
-NCU_TRAFFIC_BYTES = {"gemm_mxfp8": None, "gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(220.3e6 * 773.9 / 193.5),
+NCU_TRAFFIC_BYTES = {"gemm_mxfp8": int(223.9e6 * 781.2 / 195.3), "gemm_bf16": int(218.7e6 * 402.7 / 167.8), "gemm_fp8": int(220.3e6 * 773.9 / 193.5),
                      "attn_fwd": int(137.6e6 * 671.1 / 167.8), "attn_decode": int(690.2e6)}
 
 
