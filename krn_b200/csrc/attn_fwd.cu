@@ -158,7 +158,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
       const uint32_t idesc_s = umma_idesc(fmt, fmt, kTileQ, kTileKV, 0, 0);
       const uint32_t idesc_pv = umma_idesc(fmt, fmt, kTileQ, D, 0, 1);
@@ -177,40 +178,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       auto issue_s = [&](int t, int stage) {
         const uint32_t qa = q_lo + t * (L::kQBytes >> 4);
         const uint32_t ka = k_lo + stage * (L::kKVBytes >> 4);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * L::kBlockBytes + (ks & 3) * 32) >> 4;
-          umma_ss_halves<1, false>(tmem_base + t * 128, qa + off, kmajor_hi, ka + off, kmajor_hi, idesc_s,
-                                   ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = ((ks >> 2) * L::kBlockBytes + (ks & 3) * 32) >> 4;
+            umma_ss_halves<1, false>(tmem_base + t * 128, qa + off, kmajor_hi, ka + off, kmajor_hi, idesc_s,
+                                     ks > 0 ? 1u : 0u);
+          }
+          umma_commit(s_full + 8 * t);
         }
-        umma_commit(s_full + 8 * t);
+        __syncwarp();
       };
       // O_t += P_t V: 8 instructions of K = 16 keys; A = P_t in tensor memory (8 columns per 16 keys), B = V
       // tile with d contiguous: 64-column blocks kBlockBytes apart (leading), 8-key groups 1024 bytes apart
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t va = v_lo + stage * (L::kKVBytes >> 4);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < kTileKV / 16; ++ks) {
-          umma_ts_f16_halves(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, va + ks * (2048 >> 4), mnmajor_hi,
-                             idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kTileKV / 16; ++ks) {
+            umma_ts_f16_halves(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, va + ks * (2048 >> 4), mnmajor_hi,
+                               idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+          }
         }
+        __syncwarp();
       };
 
-      bool ok = mbar_wait(q_full, 0, abort_flag, status, kSiteMmaQ) &&
-                mbar_wait(k_full, 0, abort_flag, status, kSiteMmaK);
+      auto wait = [&](uint32_t bar, uint32_t parity, int site) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, site)) != 0;
+      };
+      bool ok = wait(q_full, 0, kSiteMmaQ) && wait(k_full, 0, kSiteMmaK);
       if (ok) {
         tc_fence_after();
         for (int t = 0; t < 2; ++t)
           if (nt[t] > 0) issue_s(t, 0);
-        umma_commit(k_empty);  // K(0) is free once both score products have read it
+        if (leader) umma_commit(k_empty);  // K(0) is free once both score products have read it
       }
       for (int j = 0; j < n && ok; ++j) {
         const int stage = j & 1;
-        if (!mbar_wait(v_full + 8 * stage, (j >> 1) & 1, abort_flag, status, kSiteMmaV)) break;
+        if (!wait(v_full + 8 * stage, (j >> 1) & 1, kSiteMmaV)) break;
         bool next_k_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= nt[t]) continue;
-          if (!mbar_wait(p_full + 8 * t, j & 1, abort_flag, status, kSiteMmaP)) {
+          if (!wait(p_full + 8 * t, j & 1, kSiteMmaP)) {
             ok = false;
             break;
           }
@@ -218,7 +227,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           issue_pv(t, stage, j > 0);
           if (j + 1 < nt[t]) {
             if (!next_k_ready) {
-              if (!mbar_wait(k_full + 8 * (stage ^ 1), ((j + 1) >> 1) & 1, abort_flag, status, kSiteMmaK)) {
+              if (!wait(k_full + 8 * (stage ^ 1), ((j + 1) >> 1) & 1, kSiteMmaK)) {
                 ok = false;
                 break;
               }
@@ -227,12 +236,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             issue_s(t, stage ^ 1);
           } else {
-            umma_commit(o_full + 8 * t);  // last P.V of this tile
+            if (leader) umma_commit(o_full + 8 * t);  // last P.V of this tile
           }
         }
         if (!ok) break;
-        umma_commit(v_empty + 8 * stage);
-        if (j + 1 < n) umma_commit(k_empty + 8 * (stage ^ 1));
+        if (leader) {
+          umma_commit(v_empty + 8 * stage);
+          if (j + 1 < n) umma_commit(k_empty + 8 * (stage ^ 1));
+        }
+        __syncwarp();
       }
     }
   } else if (warp >= 4) {

@@ -191,7 +191,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // barrier poll that succeeds at once still costs it about 250 cycles. So it polls ONE barrier per K block:
     // `full[stage]` counts the producer's arrive (with the stage's bytes) AND the promotion warps' hand-back of the
     // partial buffer this K block will overwrite (they arrive on the full barrier of the K block two ahead).
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop and one elected lane issues, so that the compiler keeps descriptors, barrier
+    // addresses and loop state in uniform registers, which tcgen05 instructions take directly.
+    if (rank == 0) {
+      const bool leader = elect_one();
       const uint32_t idesc = umma_idesc(kFmtE4M3, kFmtE4M3, kBM * CTA_GROUP, kBN);
       const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
       const uint32_t desc_hi = uint32_t(desc0 >> 32);
@@ -202,27 +205,30 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull))) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * kBN;
           const uint32_t b_lo = a_lo + (L::kABytes >> 4);
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, desc_hi, b_lo + 2 * ks, desc_hi, idesc,
-                                            ks > 0 ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_ss_halves<CTA_GROUP, true>(d_tmem, a_lo + 2 * ks, desc_hi, b_lo + 2 * ks, desc_hi, idesc,
+                                              ks > 0 ? 1u : 0u);
+            }
+            // the promotion warps wait for the first of these: it is on the kernel's critical cycle, the producer's
+            // is not
+            if constexpr (CTA_GROUP == 1) {
+              umma_commit(part_full_bar + 8 * buf);
+              umma_commit(empty_bar + 8 * stage);
+            } else {
+              umma_commit_pair(part_full_bar + 8 * buf, 0x3);
+              umma_commit_pair(empty_bar + 8 * stage, 0x3);
+            }
           }
-          // the promotion warps wait for the first of these: it is on the kernel's critical cycle (a commit costs the
-          // issuing thread 60-120 cycles), the producer's is not
-          if constexpr (CTA_GROUP == 1) {
-            umma_commit(part_full_bar + 8 * buf);
-            umma_commit(empty_bar + 8 * stage);
-          } else {
-            umma_commit_pair(part_full_bar + 8 * buf, 0x3);
-            umma_commit_pair(empty_bar + 8 * stage, 0x3);
-          }
+          __syncwarp();
           buf ^= 1u;
           a_lo += L::kStageBytes >> 4;
           if (++stage == L::kStages) {

@@ -223,7 +223,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop and one elected lane issues: on one path, the compiler keeps descriptors, barrier
+    // addresses and loop state in uniform registers, which tcgen05 instructions take directly.
+    if (rank == 0) {
+      const bool leader = elect_one();
+      auto wait = [&](uint32_t bar, uint32_t parity, int site) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, site)) != 0;
+      };
       const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
       const uint32_t desc_hi = uint32_t(desc0 >> 32);
       int stage = 0;
@@ -235,10 +241,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       // two K blocks per barrier: one poll and one commit per 256 codes of K.
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++iter) {
         // the single accumulator must have been read out by the epilogue of the previous tile
-        if (!mbar_wait(tmem_empty_bar, (iter & 1u) ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
+        if (!wait(tmem_empty_bar, (iter & 1u) ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after();
         for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+          if (!wait(full_bar + 8 * stage, phase, kSiteMmaFull)) {
             ok = false;
             break;
           }
@@ -249,49 +255,59 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t slot = chunk & 1u;
             const int in_chunk = kb & (kScaleChunk - 1);
             if (in_chunk == 0) {
-              if (!mbar_wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, abort_flag, status, kSiteMmaScale)) {
+              if (!wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, kSiteMmaScale)) {
                 ok = false;
                 break;
               }
               tc_fence_after();
             }
             const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
-            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
-            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
-            scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
-            const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
-            const uint32_t b_lo = a_lo + (kABytes >> 4);
+            const bool slot_done = in_chunk == kScaleChunk - 1 || kb == num_kb - 1;
+            if (leader) {
+              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
+              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
+              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
+              const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
+              const uint32_t b_lo = a_lo + (kABytes >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
-                                 tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
-            }
-            if (in_chunk == kScaleChunk - 1 || kb == num_kb - 1) {
-              if constexpr (CTA_GROUP == 1) {
-                umma_commit(scale_empty_bar + 8 * slot);
-              } else {
-                umma_commit_pair(scale_empty_bar + 8 * slot, 0x3);
+              for (int ks = 0; ks < 4; ++ks) {
+                umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
+                                   tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
               }
-              ++chunk;
+              if (slot_done) {
+                if constexpr (CTA_GROUP == 1) {
+                  umma_commit(scale_empty_bar + 8 * slot);
+                } else {
+                  umma_commit_pair(scale_empty_bar + 8 * slot, 0x3);
+                }
+              }
             }
+            __syncwarp();
+            if (slot_done) ++chunk;
           }
           if (!ok) break;
-          if constexpr (CTA_GROUP == 1) {
-            umma_commit(empty_bar + 8 * stage);
-          } else {
-            umma_commit_pair(empty_bar + 8 * stage, 0x3);
+          if (leader) {
+            if constexpr (CTA_GROUP == 1) {
+              umma_commit(empty_bar + 8 * stage);
+            } else {
+              umma_commit_pair(empty_bar + 8 * stage, 0x3);
+            }
           }
+          __syncwarp();
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        if constexpr (CTA_GROUP == 1) {
-          umma_commit(tmem_full_bar);
-        } else {
-          umma_commit_pair(tmem_full_bar, 0x3);
+        if (leader) {
+          if constexpr (CTA_GROUP == 1) {
+            umma_commit(tmem_full_bar);
+          } else {
+            umma_commit_pair(tmem_full_bar, 0x3);
+          }
         }
+        __syncwarp();
       }
     }
   } else if (warp < 4) {

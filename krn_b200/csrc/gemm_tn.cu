@@ -183,7 +183,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop and one elected lane issues: with every lane on the same path the compiler keeps
+    // descriptors, barrier addresses and loop state in uniform registers, which tcgen05 instructions take directly
+    // (measured: 23 against 45 cycles per product instruction, 7 against 44 per commit, when issued from a
+    // one-lane branch).
+    if (rank == 0) {
+      const bool leader = elect_one();
+      auto wait = [&](uint32_t bar, uint32_t parity, int site) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, site)) != 0;
+      };
       const uint32_t idesc = umma_idesc(a_format, b_format, kBM * CTA_GROUP, kBN, 0, p.b_kn ? 1u : 0u);
       // Descriptor words: b as (N, K) is K-major like a, 32 bytes of K per instruction inside the swizzle span; b as
       // (K, N) is an MN-major operand: blocks of 128 bytes of N are kBlockBytes apart (8192 for 16-bit, 16384 for 8-bit
@@ -202,29 +210,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
-        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status, kSiteMmaTmemEmpty)) break;
+        if (!wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kSiteMmaFull)) {
+          if (!wait(full_bar + 8 * stage, phase, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const int blocks = min(2, num_kb - kb0);
-          for (int j = 0; j < blocks; ++j) {
-            const uint32_t step = uint32_t(j) * (L::kBlockStageBytes >> 4);
+          if (leader) {
+            for (int j = 0; j < blocks; ++j) {
+              const uint32_t step = uint32_t(j) * (L::kBlockStageBytes >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              umma_ss_halves<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_lo + step + 2 * ks, a_hi, b_lo + step + b_step * ks, b_hi,
-                                                         idesc, (kb0 + j > 0 || ks > 0) ? 1u : 0u);
+              for (int ks = 0; ks < 4; ++ks) {
+                umma_ss_halves<CTA_GROUP, ELEM_BYTES == 1>(d_tmem, a_lo + step + 2 * ks, a_hi, b_lo + step + b_step * ks,
+                                                           b_hi, idesc, (kb0 + j > 0 || ks > 0) ? 1u : 0u);
+              }
+            }
+            if constexpr (CTA_GROUP == 1) {
+              umma_commit(empty_bar + 8 * stage);
+            } else {
+              umma_commit_pair(empty_bar + 8 * stage, 0x3);
             }
           }
-          if constexpr (CTA_GROUP == 1) {
-            umma_commit(empty_bar + 8 * stage);
-          } else {
-            umma_commit_pair(empty_bar + 8 * stage, 0x3);
-          }
+          __syncwarp();
           a_lo += L::kStageBytes >> 4;
           b_lo += L::kStageBytes >> 4;
           if (++stage == L::kStages) {
@@ -235,11 +246,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         if (!ok) break;
-        if constexpr (CTA_GROUP == 1) {
-          umma_commit(tmem_full_bar + 8 * acc);
-        } else {
-          umma_commit_pair(tmem_full_bar + 8 * acc, 0x3);
+        if (leader) {
+          if constexpr (CTA_GROUP == 1) {
+            umma_commit(tmem_full_bar + 8 * acc);
+          } else {
+            umma_commit_pair(tmem_full_bar + 8 * acc, 0x3);
+          }
         }
+        __syncwarp();
       }
     }
   } else {
