@@ -6,7 +6,7 @@ Headline workload: the bf16 tile product C = A @ B^T with M = N = K = 8192, f32 
 configuration the headline metric is quoted on. A "step" is one pass of the hot path over one batch of synthetic
 operands (seeded N(0,1), generated on the device). With the default `--workload all` the line also carries
 `workloads`: one sub-record with the same keys for each of the other configurations — `gemm_fp8` (block-scaled e4m3,
-8192 x 28672 x 8192), `gemm_mxfp8` (the same extents in the MXFP8 format, scales applied by the tensor cores), `attn_fwd` (causal GQA flash attention, B=8, Hq=32, Hkv=8, S=4096, D=128), `attn_decode` (paged
+8192 x 28672 x 8192), `gemm_mxfp8` and `gemm_nvfp4` (the same extents in the MXFP8 and NVFP4 formats, scales applied by the tensor cores), `attn_fwd` (causal GQA flash attention, B=8, Hq=32, Hkv=8, S=4096, D=128), `attn_decode` (paged
 FP8 decode, 64 sequences, contexts 1024..8192). `--workload NAME` measures that one alone as the headline.
 
 Timing: W (at least 3) warm-up steps, then TRIALS of exactly K steps each, every trial bracketed by a barrier and a
@@ -464,6 +464,90 @@ class GemmMxfp8(Workload):
         return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
 
 
+class GemmNvfp4(GemmMxfp8):
+    """NVFP4 product (packed e2m1 codes, one e4m3 scale per 1 x 16 block applied by the tensor cores, one f32 tensor scale
+    per matrix) at the C3 extents M=8192 N=28672 K=8192 (seed 2), bf16 out. One GPU only."""
+
+    name, metric, dtype = "gemm_nvfp4", "nvfp4_gemm_tflops", "fp4_e2m1"
+    description = "NVFP4 GEMM M=8192 N=28672 K=8192, e4m3 scales per 1x16 block fed to the block-scaled MMA, bf16 out (seed 2)"
+
+    def __init__(self, torch, rank, world, size=None) -> None:
+        Workload.__init__(self, torch, rank, world)
+        if size:
+            self.m, self.n, self.k = size
+            self.description = f"NVFP4 GEMM M={self.m} N={self.n} K={self.k} (profiling case)"
+        if world > 1:
+            raise RuntimeError("the NVFP4 product has no sharded entry point: measured on one GPU only")
+        gen = torch.Generator(device="cuda").manual_seed(2)
+        self.a, self.sa, ta = self._quantize(torch.randn((self.m, self.k), device="cuda", generator=gen))
+        self.b, self.sb, tb = self._quantize(torch.randn((self.n, self.k), device="cuda", generator=gen))
+        self.alpha = ta * tb
+        self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+
+    def _quantize(self, x):
+        """The NVFP4 rule on the device: tensor scale = absmax / (6 * 448), block scale = e4m3(block absmax / 6 / tensor
+        scale), codes = e2m1(x / (scale * tensor scale)) packed two per byte, low nibble first."""
+        torch = self.torch
+        rows, cols = x.shape
+        tensor_scale = float(x.abs().max()) / (6.0 * 448.0)
+        blocks = x.view(rows, cols // 16, 16)
+        absmax = blocks.abs().amax(dim=2)
+        scale_codes = (absmax / 6.0 / tensor_scale).clamp_(max=448.0).to(torch.float8_e4m3fn)
+        scale = scale_codes.float() * tensor_scale
+        mag = torch.where(scale[:, :, None] > 0, blocks.abs() / torch.where(scale > 0, scale, torch.ones_like(scale))[:, :, None],
+                          torch.zeros_like(blocks))
+        code = ((mag > 0.25).to(torch.uint8) + (mag >= 0.75) + (mag > 1.25) + (mag >= 1.75) + (mag > 2.5) + (mag >= 3.5) +
+                (mag > 5.0)).to(torch.uint8)
+        code |= (blocks < 0).to(torch.uint8) << 3
+        code = code.view(rows, cols)
+        packed = (code[:, 0::2] | (code[:, 1::2] << 4)).contiguous()
+        return packed, scale_codes.view(torch.uint8).contiguous(), tensor_scale
+
+    @property
+    def config(self) -> dict:
+        return {"workload": self.description, "m": self.m, "n": self.n, "k": self.k, "sharding": "one GPU, no exchange",
+                "l2": self.l2_note("operands and output", (self.m * self.k + self.n * self.k) // 2 + 2 * self.m * self.n, 1)}
+
+    def peak(self, peaks: dict) -> tuple[float, str]:
+        return 4.0 * peaks["bf16_tflops_sustained"], "4 x sustained cuBLAS bf16 (no FP4 peak was measured on this pool)"
+
+    def step(self, calls) -> None:
+        calls.gemm_nvfp4_tn(self.a, self.sa, self.b, self.sb, self.c, self.alpha, self.torch.cuda.current_stream())
+
+    kernel_only = step
+
+    def parity_sample(self, oracle, calls) -> dict:
+        import numpy as np
+
+        torch = self.torch
+        self.step(calls)
+        torch.cuda.synchronize()
+        rows = [0, 1, 127, 128, self.m // 2, self.m - 129, self.m - 128, self.m - 1]
+        host = lambda t: t.contiguous().cpu().numpy()
+        errors = []
+        for lo in (0, (self.n // 2) // 256 * 256, self.n - 256):
+            want = oracle.bf16_values(oracle.gemm_nvfp4(host(self.a[rows]), host(self.sa[rows]), host(self.b[lo:lo + 256]),
+                                                        host(self.sb[lo:lo + 256]), self.alpha, threads=8))
+            got = oracle.bf16_values(self.c[rows, lo:lo + 256].contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+            errors.append(oracle.rel_frobenius(got, want))
+        return {"value": max(errors), "tolerance": 3e-2,
+                "sample": f"{len(rows)} rows x the first, a middle and the last 256-column tile against the oracle"}
+
+    def cpu_sample(self, oracle, cores: int, columns: int | None = None):
+        import numpy as np
+
+        n = columns or 2048
+        rows = 64 * cores
+        rng = np.random.default_rng(2)
+        a, sa, ta = oracle.quantize_nvfp4(rng.standard_normal((rows, self.k), np.float32))
+        b, sb, tb = oracle.quantize_nvfp4(rng.standard_normal((n, self.k), np.float32))
+
+        def run() -> None:
+            oracle.gemm_nvfp4(a, sa, b, sb, ta * tb, threads=cores)
+
+        return 2.0 * rows * n * self.k, f"first {rows} rows x {n} columns of the product, K={self.k}, {cores} threads", run
+
+
 class AttnFwd(Workload):
     """Causal GQA flash attention forward, B=8 Hq=32 Hkv=8 S=4096 D=128, bf16 (seed 3). Sharded by batch."""
 
@@ -678,7 +762,7 @@ class AttnDecode(Workload):
         return self._bytes(tokens, cores), f"{cores} sequences with contexts U[1024,2048], {cores} threads", run
 
 
-WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, GemmMxfp8, AttnFwd, AttnDecode)}
+WORKLOADS = {w.name: w for w in (GemmBf16, GemmFp8, GemmMxfp8, GemmNvfp4, AttnFwd, AttnDecode)}
 
 
 def cpu_rates(workload, oracle, cores: int, columns: int | None, repeats: int = 1) -> dict:
@@ -803,7 +887,7 @@ class Harness:
         peak, peak_note = workload.peak(self.peaks)
         roofline = {"bound": workload.bound, "achieved": achieved, "peak": peak, "unit": workload.unit,
                     "frac": achieved / peak,
-                    "traffic": None if args.size or self.world > 1 else NCU_TRAFFIC_BYTES[workload.name],
+                    "traffic": None if args.size or self.world > 1 else NCU_TRAFFIC_BYTES.get(workload.name),
                     "peak_kind": f"{self.peak_kind}: {peak_note}", "kernel_ms": kernel_ms}
         if workload.bound == "tensor":
             # `achieved` is the median of a run of back-to-back launches that lasts long enough for the power cap to
@@ -892,7 +976,7 @@ def main() -> int:
 
     others = {}
     if args.workload == "all" and not args.size:
-        for name in ("gemm_fp8", "gemm_mxfp8", "attn_fwd", "attn_decode") if world == 1 else ("gemm_fp8", "attn_fwd", "attn_decode"):
+        for name in ("gemm_fp8", "gemm_mxfp8", "gemm_nvfp4", "attn_fwd", "attn_decode") if world == 1 else ("gemm_fp8", "attn_fwd", "attn_decode"):
             try:
                 workload = WORKLOADS[name](torch, rank, world, None)
                 # with N > 1 the sub-records carry the device-resident numbers only (the run stays within minutes)

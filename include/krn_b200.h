@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8 and krn_b200_gemm_mxfp8_tn added */
+#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8, krn_b200_gemm_mxfp8_tn and krn_b200_gemm_nvfp4_tn added */
 
 /* status codes */
 #define KRN_B200_OK 0
@@ -160,6 +160,22 @@ int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa,
  *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
 int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c, int64_t m,
                            int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                           void* stream);
+
+/* C[M,N] = alpha * sum over 16-wide K blocks kb of  sa[m,kb] * sb[n,kb] * (A4[m, kb] . B4[n, kb]): the product of two
+ * matrices in the reference's NVFP4 block format — e2m1 codes packed two per byte (low nibble first), one e4m3 scale
+ * byte per 1 x 16 block of a row, one f32 tensor scale per matrix (src/krn/data/formats.py:147-154; `QMatrix[NVFP4]`,
+ * src/krn/frontend/memory.py:255-269, whose `@` the reference declares and does not implement, :173-193). The block
+ * scales are operands of the tensor-core instruction (tcgen05.mma kind::mxf4nvf4.block_scale.scale_vec::4X); alpha,
+ * the product of the two tensor scales, multiplies the finished accumulator.
+ *   a, b    packed e2m1 codes, K-major: a [M, K / 2] bytes, b [N, K / 2] bytes; lda / ldb row pitches in BYTES,
+ *           multiples of 16
+ *   sa, sb  e4m3 bytes (sign bit clear): sa [M, K / 16], sb [N, K / 16]; ldsa / ldsb row pitches in bytes; addresses and
+ *           pitches multiples of 16
+ *   K       the number of codes per row, a multiple of 256; M, N ragged as in krn_b200_gemm_tn
+ *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
+int krn_b200_gemm_nvfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, float alpha, void* c,
+                           int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
                            void* stream);
 
 /* The block-scaled FP8 product sharded by output columns with the all-gather of the columns done by the kernel's

@@ -1,4 +1,4 @@
-// MXFP8 tile product with the block scales applied BY the tensor cores:
+// MXFP8 and NVFP4 tile products with the block scales applied BY the tensor cores. MXFP8:
 //   C[m,n] = sum over 32-wide K blocks kb of  2^(sa[m,kb] - 127) * 2^(sb[n,kb] - 127) * (A8[m, kb-block] . B8[n, kb-block])
 // A8, B8 are e4m3fn codes (K-major), sa / sb one e8m0 byte per 1 x 32 block: the reference's `MXFP8` block format
 // (src/krn/data/formats.py:138-144; `QMatrix` / `QTile` carry it as signatures only, src/krn/frontend/memory.py:173-193,
@@ -29,6 +29,14 @@
 //
 // The scale-factor columns are rewritten for every K block while earlier products may still be in flight; tcgen05.cp
 // and tcgen05.mma issued by one thread execute in issue order, which is what makes that safe.
+//
+// NVFP4 (template flag FP4; the reference's `NVFP4` block format, src/krn/data/formats.py:147-154):
+//   C[m,n] = alpha * sum over 16-wide K blocks kb of  sa[m,kb] * sb[n,kb] * (A4[m, kb-block] . B4[n, kb-block])
+// A4, B4 are e2m1 codes packed two per byte (low nibble = lower k), sa / sb one e4m3 byte per 1 x 16 block, alpha the
+// product of the two matrices' f32 tensor scales (applied in the epilogue). Same kernel, same roles; what changes:
+// a 128-byte stage row is 256 codes, an instruction (kind::mxf4nvf4, scale_vec::4X) covers 64 codes and takes all four
+// bytes of a scale-factor column, so each of the four instructions of a K block has its own three scale copies and
+// its own twelve tensor-memory columns, and a row has 16 scale bytes per K block (one 16-byte load).
 #include "gemm_common.cuh"
 
 namespace krnb {
@@ -39,31 +47,39 @@ constexpr int kBN = 256;
 constexpr int kBK = 128;          // codes per stage row = four 32-wide scale blocks
 constexpr int kThreads = 256;
 constexpr int kABytes = kBM * 128;
-constexpr int kScaleBlockBytes = 512 + 2 * 512;         // one K block: the A group, then two B groups of 128 rows
+constexpr int kScaleGroupBytes = 512 + 2 * 512;         // one set of scale copies: the A group, then two B groups of 128 rows
 constexpr int kEpilogueBytes = 4 * 2048;                // per epilogue warp: one 16-row x 128-byte store box
-template <int CTA_GROUP>
+template <int CTA_GROUP, bool FP4>
 struct Layout {
   static constexpr int kBRows = kBN / CTA_GROUP;           // rows of B this CTA loads
-  static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block of 128 codes: this CTA's A and B rows
+  static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block (128 bytes per row): this CTA's A and B rows
   static constexpr int kStageBytes = 2 * kBlockBytes;         // a stage = two K blocks behind ONE barrier
-  // K blocks of scales per ring slot. A pair takes eight (32 scale bytes per row): the peer's loaders signal the leader
-  // with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide that
-  // together with the global-memory latency behind the K blocks of the other slot; four were measured 17 % slower.
-  static constexpr int kScaleChunk = CTA_GROUP == 2 ? 8 : 4;
+  // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
+  // four instructions take four bytes each.
+  static constexpr int kScaleSets = FP4 ? 4 : 1;
+  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes;
+  // K blocks of scales per ring slot. An MXFP8 pair takes eight (32 scale bytes per row): the peer's loaders signal the
+  // leader with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide
+  // that together with the global-memory latency behind the K blocks of the other slot; four were measured 17 %
+  // slower. NVFP4 has four times the scale bytes: four K blocks per slot in a pair (with one operand stage fewer to
+  // make room), two alone.
+  static constexpr int kScaleChunk = FP4 ? (CTA_GROUP == 2 ? 4 : 2) : (CTA_GROUP == 2 ? 8 : 4);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-  static constexpr int kStages = CTA_GROUP == 2 ? 3 : 2;
+  static constexpr int kStages = (CTA_GROUP == 2 && !FP4) ? 3 : 2;
   static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
 };
 constexpr int kTmemColumns = 512;
-constexpr int kTmemScaleA = 256;                        // column of the A scale factors (4 columns)
-constexpr int kTmemScaleB = 260;                        // column of the B scale factors (8 columns)
-static_assert(Layout<1>::kSmemBytes <= 232448 && Layout<2>::kSmemBytes <= 232448, "shared memory budget");
+constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
+constexpr int kTmemScaleB = 260;                        // and 8 of B; sets are 12 columns apart
+static_assert(Layout<1, false>::kSmemBytes <= 232448 && Layout<2, false>::kSmemBytes <= 232448 &&
+              Layout<1, true>::kSmemBytes <= 232448 && Layout<2, true>::kSmemBytes <= 232448, "shared memory budget");
 
 struct MxScales {
-  const uint8_t* sa;  // [M, K / 32] e8m0
-  const uint8_t* sb;  // [N, K / 32] e8m0
+  const uint8_t* sa;  // [M, K / 32] e8m0, or [M, K / 16] e4m3 for NVFP4
+  const uint8_t* sb;  // [N, K / 32] e8m0, or [N, K / 16] e4m3
   long long ldsa, ldsb;  // row pitches in bytes
-  int vector_ok;         // both addresses and pitches are multiples of 16: a row's four K blocks come in one load
+  int vector_ok;         // both addresses and pitches are multiples of 16: 16 scale bytes of a row come in one load
+  float alpha;           // NVFP4: product of the two tensor scales, applied to the finished accumulator
 };
 
 enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
@@ -76,6 +92,30 @@ enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSit
 __device__ __forceinline__ uint32_t mx_idesc(uint32_t sub_block, uint32_t m) {
   return (sub_block << 4) | (kFmtE4M3 << 7) | (kFmtE4M3 << 10) | (uint32_t(kBN >> 3) << 17) | (1u << 23) |
          ((m >> 4) << 24) | (sub_block << 29);
+}
+
+// Instruction descriptor of kind::mxf4nvf4.block_scale.scale_vec::4X: the same fields; operand format 1 = e2m1, scale
+// format 0 = ue4m3 (the e4m3 code read as unsigned), scale ids 0 because an instruction takes all four bytes.
+__device__ __forceinline__ uint32_t nvf4_idesc(uint32_t m) {
+  return (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) | ((m >> 4) << 24);
+}
+
+template <int CTA_GROUP>
+__device__ __forceinline__ void umma_nvf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                          uint32_t scale_a_tmem, uint32_t scale_b_tmem, uint32_t accumulate) {
+  if constexpr (CTA_GROUP == 1) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  }
 }
 
 // D[tmem] (+)= (A * scale_a) * (B * scale_b): A, B shared-memory descriptors, scales in tensor memory. One thread.
@@ -112,18 +152,19 @@ __device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t sm
   }
 }
 
-template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, bool FP4, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, Problem p, MxScales scales, DeviceStatus* status) {
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
-  using L = Layout<CTA_GROUP>;
+  using L = Layout<CTA_GROUP, FP4>;
   constexpr int kStages = L::kStages;
   constexpr int kStageBytes = L::kStageBytes;
   constexpr int kBlockBytes = L::kBlockBytes;
   constexpr int kScaleChunk = L::kScaleChunk;
   constexpr int kScaleSlotBytes = L::kScaleSlotBytes;
+  constexpr int kScaleBlockBytes = L::kScaleBlockBytes;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -149,7 +190,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int first_tile = blockIdx.x / CTA_GROUP;   // this cluster's first tile
   const int tile_step = gridDim.x / CTA_GROUP;     // clusters in the grid
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_kb = p.k / kBK;
+  const int num_kb = p.k / kBK;  // p.k counts bytes of K per row: codes for MXFP8, half the codes for NVFP4
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -264,15 +305,29 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
             const bool slot_done = in_chunk == kScaleChunk - 1 || kb == num_kb - 1;
             if (leader) {
-              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
-              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
-              scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
               const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
               const uint32_t b_lo = a_lo + (kABytes >> 4);
+              if constexpr (!FP4) {
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
-                                   tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < 4; ++ks) {
+                  umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
+                                     tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+              } else {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  // each 64-code instruction has its own scale bytes, in its own tensor-memory columns
+                  const uint32_t set = block + ks * kScaleGroupBytes;
+                  const uint32_t sfa = tmem_base + kTmemScaleA + 12 * ks, sfb = tmem_base + kTmemScaleB + 12 * ks;
+                  scales_to_tmem<CTA_GROUP>(sfa, set);
+                  scales_to_tmem<CTA_GROUP>(sfb, set + 512);
+                  scales_to_tmem<CTA_GROUP>(sfb + 4, set + 1024);
+                  umma_nvf4<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, nvf4_idesc(kBM * CTA_GROUP), sfa, sfb,
+                                       (kb > 0 || ks > 0) ? 1u : 0u);
+                }
               }
               if (slot_done) {
                 if constexpr (CTA_GROUP == 1) {
@@ -339,26 +394,44 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
                                      : (long long)tn * kBN + local;
           const bool live = row < (is_a ? p.m : p.n);
-          uint32_t w[kScaleChunk];
-#pragma unroll
-          for (int j = 0; j < kScaleChunk; ++j) w[j] = 0x7f7f7f7fu;
-          if (live) {
-            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 4;
-            if (blocks_here == kScaleChunk && scales.vector_ok) {
-#pragma unroll
-              for (int q = 0; q < kScaleChunk / 4; ++q) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + q);
-                w[4 * q] = v.x, w[4 * q + 1] = v.y, w[4 * q + 2] = v.z, w[4 * q + 3] = v.w;
-              }
-            } else {
-              for (int j = 0; j < blocks_here; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
-            }
-          }
           const int group = is_a ? 0 : 1 + local / 128;
           const int in_group = local & 127;
           uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
+          if constexpr (!FP4) {
+            uint32_t w[kScaleChunk];
 #pragma unroll
-          for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
+            for (int j = 0; j < kScaleChunk; ++j) w[j] = 0x7f7f7f7fu;
+            if (live) {
+              const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 4;
+              if (blocks_here == kScaleChunk && scales.vector_ok) {
+#pragma unroll
+                for (int q = 0; q < kScaleChunk / 4; ++q) {
+                  const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + q);
+                  w[4 * q] = v.x, w[4 * q + 1] = v.y, w[4 * q + 2] = v.z, w[4 * q + 3] = v.w;
+                }
+              } else {
+                for (int j = 0; j < blocks_here; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
+          } else {
+            // 16 scale bytes per row and K block: word i belongs to the block's i-th instruction. Rows beyond the
+            // matrix get the code of 1.0 (0x38).
+#pragma unroll
+            for (int j = 0; j < kScaleChunk; ++j) {
+              uint4 v = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+              if (live && j < blocks_here) {
+                const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + (kb0 + j) * 16;
+                v = __ldg(reinterpret_cast<const uint4*>(src));
+              }
+              uint8_t* block_dst = dst + j * kScaleBlockBytes;
+              *reinterpret_cast<uint32_t*>(block_dst) = v.x;
+              *reinterpret_cast<uint32_t*>(block_dst + kScaleGroupBytes) = v.y;
+              *reinterpret_cast<uint32_t*>(block_dst + 2 * kScaleGroupBytes) = v.z;
+              *reinterpret_cast<uint32_t*>(block_dst + 3 * kScaleGroupBytes) = v.w;
+            }
+          }
         }
         fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
         __syncwarp();
@@ -436,6 +509,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           uint32_t words[32];
           tmem_ld_32x32(t_row + chunk * kChunkCols, words);
           tmem_ld_wait(words);
+          if constexpr (FP4) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) words[i] = __float_as_uint(__uint_as_float(words[i]) * scales.alpha);
+          }
           if (chunk == kChunks - 1) hand_back();
           store_chunk(chunk, words);
         }
@@ -450,6 +527,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
           tmem_ld_wait(lo, hi);
+          if constexpr (FP4) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(lo[i]) * scales.alpha);
+              hi[i] = __float_as_uint(__uint_as_float(hi[i]) * scales.alpha);
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             if constexpr (OUT_BF16) {
@@ -486,11 +570,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
-template <int CTA_GROUP, typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, bool FP4, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
            MxScales scales, cudaStream_t stream) {
-  using L = Layout<CTA_GROUP>;
-  auto kernel = gemm_mxfp8_kernel<CTA_GROUP, OutT, OUT_BF16>;
+  using L = Layout<CTA_GROUP, FP4>;
+  auto kernel = gemm_mxfp8_kernel<CTA_GROUP, FP4, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / CTA_GROUP;
@@ -511,12 +595,75 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   return KRN_B200_OK;
 }
 
-template <int CTA_GROUP>
+template <int CTA_GROUP, bool FP4>
 int launch_for_output(const DeviceContext* ctx, int c_type, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                       Problem p, MxScales scales, cudaStream_t stream) {
-  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, float, false>(ctx, ma, mb, mc, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
-  return launch<CTA_GROUP, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
+  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FP4, float, false>(ctx, ma, mb, mc, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FP4, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
+  return launch<CTA_GROUP, FP4, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
+}
+
+// Checks shared by the two entry points, the tensor maps (operand rows as bytes: 128 per K block) and the launch.
+// `k_bytes` is the length of an operand row in bytes, `scale_bytes` of a scale row.
+template <bool FP4>
+int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, float alpha, void* c,
+                         int64_t m, int64_t n, int64_t k_bytes, int64_t scale_bytes, int64_t lda, int64_t ldb, int64_t ldc,
+                         int64_t ldsa, int64_t ldsb, cudaStream_t stream) {
+  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
+  if (ldc < n || lda < k_bytes || ldb < k_bytes || ldsa < scale_bytes || ldsb < scale_bytes) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
+  }
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "TMA needs 16-byte aligned base addresses and row pitches");
+  }
+  const bool vector_ok = aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0;
+  if (FP4 && !vector_ok) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "NVFP4 scale matrices need 16-byte aligned addresses and row pitches (the 16 "
+                "scale bytes of a 256-code K step are fetched as one vector)");
+  }
+  if (!FP4 && (reinterpret_cast<uintptr_t>(sa) % 4 != 0 || reinterpret_cast<uintptr_t>(sb) % 4 != 0 || ldsa % 4 != 0 ||
+               ldsb % 4 != 0)) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "scale matrices need 4-byte aligned addresses and row pitches (the four "
+                "scale bytes of a 128-wide K step are fetched as one word)");
+  }
+  DeviceContext* ctx = current_context();
+  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
+  if (int rc = require_sm100(ctx)) return rc;
+
+  const int group = m > kBM ? 2 : 1;  // a single 128-row panel has nothing for a second CTA to do
+  Problem p;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k_bytes);
+  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
+  p.tiles_n = int((n + kBN - 1) / kBN);
+  p.b_kn = 0;
+  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, alpha};
+
+  CUtensorMap map_a, map_b, map_c;
+  {
+    uint64_t dims[2] = {uint64_t(k_bytes), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(lda)};
+    uint32_t box[2] = {128, uint32_t(kBM)};
+    if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(k_bytes), uint64_t(n)};
+    uint64_t strides[1] = {uint64_t(ldb)};
+    uint32_t box[2] = {128, uint32_t(kBN / group)};
+    if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  {
+    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
+    uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
+    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  }
+  if (group == 2) return launch_for_output<2, FP4>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  return launch_for_output<1, FP4>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
 }
 
 }  // namespace
@@ -542,54 +689,29 @@ extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* 
   if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
-  const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
-  const int64_t blocks_k = k / 32;
-  if (ldc < n || lda < k || ldb < k || ldsa < blocks_k || ldsb < blocks_k) {
-    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
-  }
-  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
-    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "TMA needs 16-byte aligned base addresses and row pitches");
-  }
-  if (reinterpret_cast<uintptr_t>(sa) % 4 != 0 || reinterpret_cast<uintptr_t>(sb) % 4 != 0 || ldsa % 4 != 0 || ldsb % 4 != 0) {
-    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "scale matrices need 4-byte aligned addresses and row pitches (the four "
-                "scale bytes of a 128-wide K step are fetched as one word)");
-  }
-  DeviceContext* ctx = current_context();
-  if (ctx == nullptr) return KRN_B200_ERR_CUDA;
-  if (int rc = require_sm100(ctx)) return rc;
+  return block_scaled_product<false>(c_type, a, sa, b, sb, 1.0f, c, m, n, k, k / 32, lda, ldb, ldc, ldsa, ldsb, stream);
+}
 
-  const int group = m > kBM ? 2 : 1;  // a single 128-row panel has nothing for a second CTA to do
-  Problem p;
-  p.m = int(m);
-  p.n = int(n);
-  p.k = int(k);
-  p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
-  p.tiles_n = int((n + kBN - 1) / kBN);
-  p.b_kn = 0;
-  MxScales scales = {sa, sb, ldsa, ldsb, (aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0) ? 1 : 0};
-
-  CUtensorMap map_a, map_b, map_c;
-  {
-    uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
-    uint64_t strides[1] = {uint64_t(lda)};
-    uint32_t box[2] = {128, uint32_t(kBM)};
-    if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, Swizzle::k128B)) return rc;
+extern "C" int krn_b200_gemm_nvfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb,
+                                      float alpha, void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                      int64_t ldc, int64_t ldsa, int64_t ldsb, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
   }
-  {
-    uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
-    uint64_t strides[1] = {uint64_t(ldb)};
-    uint32_t box[2] = {128, uint32_t(kBN / group)};
-    if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, Swizzle::k128B)) return rc;
+  if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent");
+  if (m == 0 || n == 0) return KRN_B200_OK;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
   }
-  {
-    const CUtensorMapDataType c_dt = c_type == KRN_B200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                     : c_type == KRN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
-    uint64_t strides[1] = {uint64_t(ldc) * c_bytes};
-    uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
-    if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
+  if (k == 0 || k % 256 != 0) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "NVFP4 product with K = %lld is not available on sm_100a: the kernel consumes "
+                "256 codes (128 bytes, sixteen 16-wide scale blocks) per step. Instead: pad K to a multiple of 256 with zero "
+                "codes", (long long)k);
   }
-  if (group == 2) return launch_for_output<2>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
-  return launch_for_output<1>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  return block_scaled_product<true>(c_type, a, sa, b, sb, alpha, c, m, n, k / 2, k / 16, lda, ldb, ldc, ldsa, ldsb, stream);
 }

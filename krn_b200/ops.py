@@ -37,9 +37,10 @@ def matmul(a: Any, b: Any, out: Any, stream: Any = None) -> Any:
 class QMatrix:
     """A block-scaled matrix on the device, with the fields of the reference's `QMatrix[F]` struct
     (src/krn/frontend/memory.py:255-269): the block format `fmt` (a `krn_b200.formats.BlockFormat`: `FP8FN()`,
-    `FP8FNWeights()` or `MXFP8()`), the logical `shape`, the `codes` (one byte per element, (rows, K), K contiguous —
-    blocks run along the contraction axis), the `scales` (f32 for the FP8FN formats, e8m0 bytes for MXFP8; one per
-    block) and an optional per-tensor `tensor_scale` (used by formats that define one; none of the three here does)."""
+    `FP8FNWeights()`, `MXFP8()` or `NVFP4()`), the logical `shape`, the `codes` ((rows, K), K contiguous — blocks run
+    along the contraction axis; one byte per element, or for NVFP4 two 4-bit codes per byte, low nibble first), the
+    `scales` (f32 for the FP8FN formats, e8m0 bytes for MXFP8, e4m3 bytes for NVFP4; one per block) and the per-tensor
+    `tensor_scale` of formats that define one (NVFP4: a float)."""
 
     fmt: Any
     shape: tuple[int, int]
@@ -60,6 +61,42 @@ def _e4m3_codes(values: np.ndarray) -> np.ndarray:
 
     clipped = np.clip(values.astype(np.float32), -448.0, 448.0)
     return clipped.astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
+
+
+_E2M1_MAX = 6.0
+
+
+def _e2m1_codes(values: np.ndarray) -> np.ndarray:
+    """4-bit e2m1 codes (magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6): nearest, ties to the code with an even mantissa bit,
+    saturating — the same narrowing rule as `_e4m3_codes`, written as the seven rounding thresholds of the format."""
+    mag = np.abs(values.astype(np.float32))
+    code = ((mag > 0.25).astype(np.uint8) + (mag >= 0.75) + (mag > 1.25) + (mag >= 1.75) + (mag > 2.5) + (mag >= 3.5) +
+            (mag > 5.0)).astype(np.uint8)
+    return code | (np.signbit(values).astype(np.uint8) << 3)
+
+
+def quantize_nvfp4_host(values: np.ndarray) -> tuple[np.ndarray, np.ndarray, float]:
+    """(packed codes (rows, K / 2), e4m3 scale bytes (rows, K / 16), tensor scale) of a float32 host matrix in the NVFP4
+    format (src/krn/data/formats.py:147-154): the f32 tensor scale maps the largest block scale onto 448 (the largest
+    e4m3 value), a block's scale is absmax / 6 / tensor_scale rounded to e4m3 (`ScaleRounding.NEAREST`), and the codes
+    are x / (scale * tensor_scale) rounded to e2m1, two per byte with the lower column in the low nibble (`Storage.X2`).
+    Blocks whose scale rounds to zero store zero codes."""
+    values = np.ascontiguousarray(values, np.float32)
+    rows, cols = values.shape
+    if cols % 16:
+        raise ValueError(f"cannot quantize a {rows} x {cols} matrix to nvfp4: rows must be whole 1 x 16 blocks")
+    largest = float(np.abs(values).max()) if values.size else 0.0
+    tensor_scale = np.float32(largest / (_E2M1_MAX * 448.0)) if largest > 0 else np.float32(1.0)
+    blocks = values.reshape(rows, cols // 16, 16)
+    absmax = np.abs(blocks).max(axis=2)
+    scale_codes = _e4m3_codes(absmax / np.float32(_E2M1_MAX) / tensor_scale)
+    import ml_dtypes
+
+    scale = scale_codes.view(ml_dtypes.float8_e4m3fn).astype(np.float32) * tensor_scale
+    safe = np.where(scale > 0, scale, np.float32(1.0))
+    codes = _e2m1_codes(np.where(scale[:, :, None] > 0, blocks / safe[:, :, None], np.float32(0.0))).reshape(rows, cols)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    return np.ascontiguousarray(packed), np.ascontiguousarray(scale_codes), float(tensor_scale)
 
 
 def quantize_host(values: np.ndarray, fmt: Any) -> tuple[np.ndarray, np.ndarray]:
@@ -94,27 +131,36 @@ def quantize_host(values: np.ndarray, fmt: Any) -> tuple[np.ndarray, np.ndarray]
 def quantize(values: np.ndarray, fmt: Any, device: Any = None) -> QMatrix:
     """Convert a float32 host matrix (rows, K) to `fmt` (see `quantize_host`) and place it on the device — what the
     reference's `Resolution.quantize(weights) -> QMatrix[F]` is declared to do (src/krn/frontend/precision.py:43-45)."""
+    from krn_b200 import formats
+
     device = device or default_device()
+    if isinstance(fmt, formats.NVFP4):
+        packed, scale_codes, tensor_scale = quantize_nvfp4_host(values)
+        return QMatrix(fmt, tuple(values.shape), device.to_device(packed), device.to_device(scale_codes), tensor_scale)
     codes, stored = quantize_host(values, fmt)
     return QMatrix(fmt, tuple(values.shape), device.to_device(codes, f8e4m3fn), device.to_device(stored))
 
 
 def matmul_q(a: QMatrix, b: QMatrix, out: Any, stream: Any = None) -> Any:
     """out[M, N] = a @ b^T for two block-scaled matrices whose blocks run along K (both stored (rows, K)) — the product
-    the reference declares as `QTile.__matmul__` (src/krn/frontend/memory.py:173-193). Two pairings have kernels:
+    the reference declares as `QTile.__matmul__` (src/krn/frontend/memory.py:173-193). Three pairings have kernels:
     FP8FN activations (1 x 128 f32 scales) with FP8FNWeights (128 x 128 f32 scales), whose partial sums are scaled as they
-    are accumulated, and MXFP8 with MXFP8, whose scales the tensor cores apply themselves."""
+    are accumulated, and MXFP8 with MXFP8 and NVFP4 with NVFP4, whose block scales the tensor cores apply themselves."""
     from krn_b200 import formats
 
     if a.shape[1] != b.shape[1]:
         raise ValueError(f"contraction lengths differ: {a.shape} @ {b.shape}^T")
     if isinstance(a.fmt, formats.MXFP8) and isinstance(b.fmt, formats.MXFP8):
         calls.gemm_mxfp8_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
+    elif isinstance(a.fmt, formats.NVFP4) and isinstance(b.fmt, formats.NVFP4):
+        alpha = float(a.tensor_scale if a.tensor_scale is not None else 1.0) * float(
+            b.tensor_scale if b.tensor_scale is not None else 1.0)
+        calls.gemm_nvfp4_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), alpha, _stream(stream))
     elif a.fmt.block == (1, 128) and b.fmt.block == (128, 128) and a.fmt.scale == formats.FP32 and b.fmt.scale == formats.FP32:
         calls.gemm_fp8_blockscaled_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
     else:
         raise TargetError(f"the product {a.fmt.name} @ {b.fmt.name}", "sm_100a", "no prebuilt kernel multiplies this pair "
-                          "of block formats", "use FP8FN activations with FP8FNWeights, or MXFP8 with MXFP8")
+                          "of block formats", "use FP8FN activations with FP8FNWeights, MXFP8 with MXFP8, or NVFP4 with NVFP4")
     return out
 
 

@@ -339,6 +339,53 @@ void krn_oracle_gemm_mxfp8(int c_type, const uint8_t* a, const uint8_t* sa, cons
   free(total);
 }
 
+/* ---- NVFP4 product (the reference's NVFP4 format; its product is declared, not implemented: parity unpinned) ---- */
+
+/* e2m1 code (4 bits: sign, two exponent bits, one mantissa bit; bias 1, subnormal 0.5, every code a number:
+ * src/krn/data/formats.py:100,59-76) -> value: 0, 0.5, 1, 1.5, 2, 3, 4, 6 and their negatives. */
+float krn_oracle_e2m1_decode(uint8_t code) {
+  static const float magnitude[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  float v = magnitude[code & 7];
+  return (code & 8) ? -v : v;
+}
+
+/* C[i,j] = alpha * sum over 16-wide K blocks kb of (sa[i,kb] * sb[j,kb]) * P_kb[i,j]: a, b hold two e2m1 codes per byte,
+ * the lower k in the low nibble; sa, sb are e4m3 codes; P_kb is the sum of the block's 16 products (exact in f32, as is
+ * the product of the two scales and its multiplication into P_kb); the scaled partials are added in kb order in f32 and
+ * the total is multiplied by alpha. Rows [row_begin, row_end). lda / ldb in bytes. */
+void krn_oracle_gemm_nvfp4(int c_type, const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb, float alpha,
+                           void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa,
+                           int64_t ldsb, int64_t row_begin, int64_t row_end) {
+  (void)m;
+  float* bt = aligned_alloc(64, ((size_t)(k > 0 ? k : 1) * n * 4 + 63) / 64 * 64);
+  float* part = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  float* total = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  for (int64_t kk = 0; kk < k; ++kk)
+    for (int64_t j = 0; j < n; ++j) bt[kk * n + j] = krn_oracle_e2m1_decode((uint8_t)((b[j * ldb + kk / 2] >> (4 * (kk & 1))) & 15));
+  for (int64_t i = row_begin; i < row_end; ++i) {
+    for (int64_t j = 0; j < n; ++j) total[j] = 0.0f;
+    for (int64_t k0 = 0, kb = 0; k0 < k; k0 += 16, ++kb) {
+      int64_t k1 = k0 + 16 < k ? k0 + 16 : k;
+      for (int64_t j = 0; j < n; ++j) part[j] = 0.0f;
+      for (int64_t kk = k0; kk < k1; ++kk) {
+        float av = krn_oracle_e2m1_decode((uint8_t)((a[i * lda + kk / 2] >> (4 * (kk & 1))) & 15));
+        const float* brow = bt + kk * n;
+        for (int64_t j = 0; j < n; ++j) part[j] = __builtin_fmaf(av, brow[j], part[j]);
+      }
+      float sai = krn_oracle_e4m3_decode(sa[i * ldsa + kb]);
+      for (int64_t j = 0; j < n; ++j) {
+        float scale = sai * krn_oracle_e4m3_decode(sb[j * ldsb + kb]);
+        float scaled = scale * part[j];
+        total[j] = total[j] + scaled;
+      }
+    }
+    for (int64_t j = 0; j < n; ++j) store_from_f32(c, c_type, i * ldc + j, alpha * total[j]);
+  }
+  free(bt);
+  free(part);
+  free(total);
+}
+
 /* ---- flash attention, statement by statement --------------------------------------------------------- */
 
 static inline float krn_max(float a, float b) { return (a > b || a != a) ? a : b; } /* emit.py:116-120 */

@@ -52,13 +52,15 @@ def lib() -> ctypes.CDLL:
         handle.krn_oracle_gemm_fast.argtypes = [i32, i32, i32, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_fp8_blockscaled.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_mxfp8.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
+        handle.krn_oracle_gemm_nvfp4.argtypes = [i32, ptr, ptr, ptr, ptr, ctypes.c_float, ptr, i64, i64, i64, i64, i64, i64, i64,
+                                                 i64, i64, i64]
         handle.krn_oracle_flash_attention.argtypes = [i32, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i32, f32, i32, i32, i32, i64, i64]
         handle.krn_oracle_decode_fp8_paged.argtypes = [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i64, i32, i32, i64, f32, i64, i64]
         handle.krn_oracle_e4m3_encode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_e4m3_decode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_bf16_round_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_matmul_epilogue.argtypes = [i32, ptr, ptr, ptr, i64, i64, i32]
-        for name in ("gemm_mxfp8", "matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
+        for name in ("gemm_mxfp8", "gemm_nvfp4", "matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
                      "e4m3_encode_array", "e4m3_decode_array", "bf16_round_array"):
             getattr(handle, f"krn_oracle_{name}").restype = None
         _LIB = handle
@@ -205,6 +207,78 @@ def quantize_mxfp8(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
 def mxfp8_values(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     """float64 values of an MXFP8 matrix."""
     return e4m3_decode(codes).astype(np.float64) * np.repeat(np.exp2(scales.astype(np.float64) - 127), 32, axis=1)
+
+
+E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32)
+
+
+def e2m1_decode(codes: np.ndarray) -> np.ndarray:
+    """float32 values of 4-bit e2m1 codes (src/krn/data/formats.py:100)."""
+    codes = np.asarray(codes, np.uint8)
+    return np.where(codes & 8, -E2M1_VALUES[codes & 7], E2M1_VALUES[codes & 7]).astype(np.float32)
+
+
+def e2m1_encode(x: np.ndarray) -> np.ndarray:
+    """Nearest e2m1 code, ties to the code with an even mantissa bit, saturating at 6 (the reference's encoding rule
+    for narrow formats, src/krn/compiler/narrow.py:84-110, applied to this format)."""
+    x = np.asarray(x, np.float32)
+    mag = np.abs(x)
+    code = ((mag > 0.25).astype(np.uint8) + (mag >= 0.75) + (mag > 1.25) + (mag >= 1.75) + (mag > 2.5) + (mag >= 3.5) +
+            (mag > 5.0)).astype(np.uint8)
+    return (code | (np.signbit(x).astype(np.uint8) << 3)).astype(np.uint8)
+
+
+def pack_nibbles(codes: np.ndarray) -> np.ndarray:
+    """Two 4-bit codes per byte along the last axis, the lower index in the low nibble (`Storage.X2`)."""
+    codes = np.asarray(codes, np.uint8)
+    return (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_nibbles(packed: np.ndarray) -> np.ndarray:
+    packed = np.asarray(packed, np.uint8)
+    out = np.empty(packed.shape[:-1] + (2 * packed.shape[-1],), np.uint8)
+    out[..., 0::2], out[..., 1::2] = packed & 15, packed >> 4
+    return out
+
+
+def quantize_nvfp4(x: np.ndarray) -> tuple[np.ndarray, np.ndarray, float]:
+    """(packed e2m1 codes, e4m3 scale bytes per 1 x 16 block, f32 tensor scale) of the reference's NVFP4 format
+    (src/krn/data/formats.py:147-154: scale format e4m3fn, tensor scale f32, `ScaleRounding.NEAREST`): the tensor
+    scale maps the largest block scale onto 448, a block's scale is amax / 6 / tensor_scale rounded to e4m3, elements
+    are x / (scale * tensor_scale) rounded to e2m1."""
+    rows, cols = x.shape
+    if cols % 16:
+        raise ValueError("the row length must be a multiple of 16")
+    x = np.ascontiguousarray(x, np.float32)
+    amax_all = float(np.abs(x).max()) if x.size else 0.0
+    tensor_scale = np.float32(amax_all / (6.0 * 448.0)) if amax_all > 0 else np.float32(1.0)
+    blocks = x.reshape(rows, cols // 16, 16)
+    amax = np.abs(blocks).max(axis=2)
+    scale_codes = e4m3_encode((amax / np.float32(6.0) / tensor_scale).astype(np.float32))
+    scale = e4m3_decode(scale_codes).astype(np.float32) * tensor_scale
+    safe = np.where(scale > 0, scale, np.float32(1.0))
+    codes = e2m1_encode(np.where(scale[:, :, None] > 0, blocks / safe[:, :, None], np.float32(0.0)))
+    return pack_nibbles(codes.reshape(rows, cols)), scale_codes.astype(np.uint8), float(tensor_scale)
+
+
+def nvfp4_values(packed: np.ndarray, scales: np.ndarray, tensor_scale: float) -> np.ndarray:
+    """float64 values of an NVFP4 matrix."""
+    values = e2m1_decode(unpack_nibbles(packed)).astype(np.float64)
+    return values * np.repeat(e4m3_decode(scales).astype(np.float64), 16, axis=1) * float(tensor_scale)
+
+
+def gemm_nvfp4(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.ndarray, alpha: float = 1.0, *, c_type: int = BF16,
+               threads: int = 1) -> np.ndarray:
+    """C = alpha * sum over 16-wide K blocks of sa sb (a4 . b4): a (M, K/2), b (N, K/2) packed e2m1 codes, sa (M, K/16),
+    sb (N, K/16) e4m3 bytes."""
+    a, b = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(b, np.uint8)
+    sa, sb = np.ascontiguousarray(sa, np.uint8), np.ascontiguousarray(sb, np.uint8)
+    (m, k_bytes), n = a.shape, b.shape[0]
+    c = np.zeros((m, n), _NUMPY[c_type])
+    _run(_split(m, threads), lambda lo, hi: lib().krn_oracle_gemm_nvfp4(
+        c_type, _p(a), _p(sa), _p(b), _p(sb), float(alpha), _p(c), m, n, 2 * k_bytes, k_bytes, k_bytes, n, sa.shape[1],
+        sb.shape[1], lo, hi))
+    return c
 
 
 def quantize_blocks(x: np.ndarray, block: tuple[int, int]) -> tuple[np.ndarray, np.ndarray]:

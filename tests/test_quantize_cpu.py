@@ -53,3 +53,30 @@ def test_quantiser_refusals() -> None:
         ops.quantize_host(np.zeros((4, 48), np.float32), krn.formats.MXFP8())
     with pytest.raises(ValueError, match="e4m3fn elements"):
         ops.quantize_host(np.zeros((4, 64), np.float32), krn.formats.NVFP4())
+
+
+def test_nvfp4_quantiser_matches_the_oracle_and_the_format_tables() -> None:
+    """The product side's NVFP4 quantiser and the oracle's agree code for code; the e2m1 and e4m3 values both use are the
+    format tables (`krn.formats.E2M1`, `E4M3FN`: the reference's src/krn/data/formats.py:95,100)."""
+    x = np.random.default_rng(14).standard_normal((24, 256)).astype(np.float32) * 3
+    packed, scales, tensor_scale = ops.quantize_nvfp4_host(x)
+    want_packed, want_scales, want_tensor = o.quantize_nvfp4(x)
+    np.testing.assert_array_equal(packed, want_packed)
+    np.testing.assert_array_equal(scales, want_scales)
+    assert tensor_scale == want_tensor
+    assert [float(v) for v in o.e2m1_decode(np.arange(16))] == [float(v) for v in krn.formats.E2M1.table]
+    codes = o.unpack_nibbles(packed)
+    table = np.array(krn.formats.E2M1.table)
+    scale_table = np.array(krn.formats.E4M3FN.table)
+    values = table[codes] * np.repeat(scale_table[scales], 16, axis=1) * tensor_scale
+    np.testing.assert_allclose(values, o.nvfp4_values(packed, scales, tensor_scale), rtol=1e-7)
+    # 4-bit elements with an e4m3 scale per 16: the block maximum is reproduced to the scale's precision (6.25 %), the rest
+    # to half a step of the element grid
+    assert np.linalg.norm(values - x) / np.linalg.norm(x) < 0.12
+    # every e2m1 magnitude is its own code, ties go to the even mantissa bit
+    grid = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32)
+    np.testing.assert_array_equal(o.e2m1_decode(o.e2m1_encode(grid)), grid)
+    np.testing.assert_array_equal(o.e2m1_decode(o.e2m1_encode(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -9.0], np.float32))),
+                                  np.array([0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0, -6.0], np.float32))
+    with pytest.raises(ValueError, match="whole 1 x 16 blocks"):
+        ops.quantize_nvfp4_host(np.zeros((4, 24), np.float32))
