@@ -893,11 +893,11 @@ class Harness:
             # `achieved` is the median of a run of back-to-back launches that lasts long enough for the power cap to
             # settle the clock, so its denominator is the cuBLAS figure measured the same way (sustained); the best trial
             # (launches on a cool part) is set against the cuBLAS best-of-10 burst figure
-            factor = 2.0 if workload.dtype.startswith("fp8") else 1.0
+            factor = 4.0 if workload.dtype.startswith("fp4") else 2.0 if workload.dtype.startswith("fp8") else 1.0
             burst = factor * self.peaks["bf16_tflops"]
             roofline["burst"] = {"achieved": best, "peak": burst, "frac": best / burst,
                                  "note": "best trial over the burst (best-of-10) cuBLAS figure"}
-            roofline["frac_of_nominal_dense_peak"] = achieved / (4500.0 if factor == 2.0 else 2250.0)
+            roofline["frac_of_nominal_dense_peak"] = achieved / (2250.0 * factor)
             roofline["best_frac_of_nominal_dense_peak"] = best / (4500.0 if factor == 2.0 else 2250.0)
 
         record = {"metric": workload.metric, "value": value, "unit": workload.unit, "ms_per_step": ms_per_step,
