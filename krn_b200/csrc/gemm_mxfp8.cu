@@ -66,7 +66,10 @@ struct Layout {
   static constexpr int kScaleChunk = FP4 ? (CTA_GROUP == 2 ? 4 : 2) : (CTA_GROUP == 2 ? 8 : 4);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
   static constexpr int kStages = (CTA_GROUP == 2 && !FP4) ? 3 : 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
+  // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
+  // cluster-scope arrive) does not fit behind one slot of four K blocks.
+  static constexpr int kScaleSlots = (FP4 && CTA_GROUP == 2) ? 3 : 2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
 };
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
@@ -165,6 +168,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   constexpr int kScaleChunk = L::kScaleChunk;
   constexpr int kScaleSlotBytes = L::kScaleSlotBytes;
   constexpr int kScaleBlockBytes = L::kScaleBlockBytes;
+  constexpr int kScaleSlots = L::kScaleSlots;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -173,15 +177,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   const uint32_t stages_addr = base;
   const uint32_t scale_addr = base + kStages * kStageBytes;
-  const uint32_t epilogue_addr = scale_addr + 2 * kScaleSlotBytes;
-  uint8_t* tail = smem + kStages * kStageBytes + 2 * kScaleSlotBytes + kEpilogueBytes;
+  const uint32_t epilogue_addr = scale_addr + kScaleSlots * kScaleSlotBytes;
+  uint8_t* tail = smem + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kEpilogueBytes;
   const uint32_t full_bar = smem_u32(tail);                  // [kStages]
   const uint32_t empty_bar = full_bar + 8 * kStages;         // [kStages]
-  const uint32_t scale_full_bar = empty_bar + 8 * kStages;   // [2]
-  const uint32_t scale_empty_bar = scale_full_bar + 16;      // [2]
-  const uint32_t tmem_full_bar = scale_empty_bar + 16;
+  const uint32_t scale_full_bar = empty_bar + 8 * kStages;            // [kScaleSlots]
+  const uint32_t scale_empty_bar = scale_full_bar + 8 * kScaleSlots;  // [kScaleSlots]
+  const uint32_t tmem_full_bar = scale_empty_bar + 8 * kScaleSlots;
   const uint32_t tmem_empty_bar = tmem_full_bar + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 6));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -197,7 +201,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kScaleSlots; ++s) {
       mbar_init(scale_full_bar + 8 * s, 2 * CTA_GROUP);  // the two loader warps of every CTA of the tile
       mbar_init(scale_empty_bar + 8 * s, 1);             // the issuing thread's commit
     }
@@ -274,7 +278,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint64_t desc0 = umma_desc_kmajor_sw128(stages_addr);
       const uint32_t desc_hi = uint32_t(desc0 >> 32);
       int stage = 0;
-      uint32_t phase = 0, chunk = 0, iter = 0;
+      uint32_t phase = 0, iter = 0;
+      uint32_t slot = 0, slot_phase = 0;  // position in the ring of scale slots
       bool ok = true;
       // This thread is the kernel's critical path: every tcgen05 instruction it issues costs about 60 cycles and a
       // barrier poll about 220 even when it succeeds at once (cycle trace with one K block per barrier: 851 cycles per K
@@ -293,10 +298,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int blocks = min(2, num_kb - kb0);
           for (int j = 0; j < blocks && ok; ++j) {
             const int kb = kb0 + j;
-            const uint32_t slot = chunk & 1u;
             const int in_chunk = kb & (kScaleChunk - 1);
             if (in_chunk == 0) {
-              if (!wait(scale_full_bar + 8 * slot, (chunk >> 1) & 1u, kSiteMmaScale)) {
+              if (!wait(scale_full_bar + 8 * slot, slot_phase, kSiteMmaScale)) {
                 ok = false;
                 break;
               }
@@ -338,7 +342,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               }
             }
             __syncwarp();
-            if (slot_done) ++chunk;
+            if (slot_done && ++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
           }
           if (!ok) break;
           if (leader) {
@@ -371,21 +375,41 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // six per thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
     // group. Rows beyond the matrix get the code of 2^0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
-    uint32_t chunk = 0;
+    uint32_t slot = 0, slot_phase = 0;
     bool ok = true;
     const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
     for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       int tm, tn;
       tile_coords(t, p, tm, tn);
-      for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk) {
-        const uint32_t slot = chunk & 1u;
-        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, ((chunk >> 1) & 1u) ^ 1u, abort_flag, status,
+      for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk) {
+        const int blocks_here = min(kScaleChunk, num_kb - kb0);
+        // NVFP4: the 16-byte loads of the whole slot are issued before the wait for the slot, so that their latency
+        // runs beside the products still reading it (a slot is four K blocks only, there is four times the data)
+        uint4 early[FP4 ? 6 : 1][FP4 ? kScaleChunk : 1];
+        if constexpr (FP4) {
+#pragma unroll
+          for (int i = 0; i < 6; ++i) {
+            const int r = tid + i * 64;
+            const bool is_a = r < kBM;
+            const int local = is_a ? r : r - kBM;
+            const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
+                                       : (long long)tn * kBN + local;
+            const bool live = row < (is_a ? p.m : p.n);
+            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 16;
+#pragma unroll
+            for (int j = 0; j < kScaleChunk; ++j) {
+              // rows beyond the matrix get the code of 1.0 (0x38)
+              early[i][j] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+              if (live && j < blocks_here) early[i][j] = __ldg(reinterpret_cast<const uint4*>(src) + j);
+            }
+          }
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
                                                kSiteScaleEmpty))) {
           ok = false;
           break;
         }
         uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-        const int blocks_here = min(kScaleChunk, num_kb - kb0);
 #pragma unroll
         for (int i = 0; i < 6; ++i) {
           const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
@@ -416,15 +440,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
             for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
           } else {
-            // 16 scale bytes per row and K block: word i belongs to the block's i-th instruction. Rows beyond the
-            // matrix get the code of 1.0 (0x38).
+            // 16 scale bytes per row and K block: word i belongs to the block's i-th instruction
 #pragma unroll
             for (int j = 0; j < kScaleChunk; ++j) {
-              uint4 v = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
-              if (live && j < blocks_here) {
-                const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + (kb0 + j) * 16;
-                v = __ldg(reinterpret_cast<const uint4*>(src));
-              }
+              const uint4 v = early[i][j];
               uint8_t* block_dst = dst + j * kScaleBlockBytes;
               *reinterpret_cast<uint32_t*>(block_dst) = v.x;
               *reinterpret_cast<uint32_t*>(block_dst + kScaleGroupBytes) = v.y;
@@ -442,6 +461,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_arrive(scale_full_bar + 8 * slot);
           }
         }
+        if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
       }
     }
   } else {
