@@ -339,11 +339,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // rows beyond M hold a zero scale in the ring, so their accumulators stay zero
         const float scale = my_scales[slot * (kScaleChunk * kBM) + in_chunk * kBM] * next_sb;
         if (kb + 1 < num_kb && nb_ok) next_sb = __ldg(sb_row + kb + 1);
-        if (!__all_sync(0xffffffffu,
-                        mbar_wait(part_full_bar + 8 * buf, (it >> 1) & 1u, abort_flag, status, kSitePromotionFull))) {
+        // every lane polls the same barrier and gets the same answer: no vote (it is on this warp's critical chain)
+        if (!mbar_wait(part_full_bar + 8 * buf, (it >> 1) & 1u, abort_flag, status, kSitePromotionFull)) {
           ok = false;
           break;
         }
+        __syncwarp();
         tc_fence_after();
         const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kBN + half * 128;
         uint32_t p0[32], p1[32];
