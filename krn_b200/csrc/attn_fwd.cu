@@ -320,24 +320,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       // p = exp2(s * scale - m_ref), summed in f32 before the rounding to the storage type
       const float neg_m = -m_ref;
-      float sum = 0.f;
+      // packed f32x2 arithmetic for the scale-and-shift and the row sum: half the instructions beside the exponentials
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(neg_m, neg_m);
+      float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, sum_c = sum_a, sum_d = sum_a;
       uint32_t packed0[32], packed1[32];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float a0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, neg_m));
-        const float a1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, neg_m));
-        const float b0 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, neg_m));
-        const float b1 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, neg_m));
-        const float c0 = ex2_approx(fmaf(__uint_as_float(s2[2 * i]), p.scale_log2, neg_m));
-        const float c1 = ex2_approx(fmaf(__uint_as_float(s2[2 * i + 1]), p.scale_log2, neg_m));
-        const float d0 = ex2_approx(fmaf(__uint_as_float(s3[2 * i]), p.scale_log2, neg_m));
-        const float d1 = ex2_approx(fmaf(__uint_as_float(s3[2 * i + 1]), p.scale_log2, neg_m));
-        sum += ((a0 + a1) + (b0 + b1)) + ((c0 + c1) + (d0 + d1));
-        packed0[i] = BF16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
-        packed0[16 + i] = BF16 ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
-        packed1[i] = BF16 ? pack_bf16x2(c0, c1) : pack_f16x2(c0, c1);
-        packed1[16 + i] = BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
+        const float2 xa = __ffma2_rn(make_float2(__uint_as_float(s0[2 * i]), __uint_as_float(s0[2 * i + 1])), scale2, shift2);
+        const float2 xb = __ffma2_rn(make_float2(__uint_as_float(s1[2 * i]), __uint_as_float(s1[2 * i + 1])), scale2, shift2);
+        const float2 xc = __ffma2_rn(make_float2(__uint_as_float(s2[2 * i]), __uint_as_float(s2[2 * i + 1])), scale2, shift2);
+        const float2 xd = __ffma2_rn(make_float2(__uint_as_float(s3[2 * i]), __uint_as_float(s3[2 * i + 1])), scale2, shift2);
+        const float2 a = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
+        const float2 b2 = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
+        const float2 c = make_float2(ex2_approx(xc.x), ex2_approx(xc.y));
+        const float2 d2 = make_float2(ex2_approx(xd.x), ex2_approx(xd.y));
+        sum_a = __fadd2_rn(sum_a, a);
+        sum_b = __fadd2_rn(sum_b, b2);
+        sum_c = __fadd2_rn(sum_c, c);
+        sum_d = __fadd2_rn(sum_d, d2);
+        packed0[i] = BF16 ? pack_bf16x2(a.x, a.y) : pack_f16x2(a.x, a.y);
+        packed0[16 + i] = BF16 ? pack_bf16x2(b2.x, b2.y) : pack_f16x2(b2.x, b2.y);
+        packed1[i] = BF16 ? pack_bf16x2(c.x, c.y) : pack_f16x2(c.x, c.y);
+        packed1[16 + i] = BF16 ? pack_bf16x2(d2.x, d2.y) : pack_f16x2(d2.x, d2.y);
       }
+      const float2 sum2 = __fadd2_rn(__fadd2_rn(sum_a, sum_b), __fadd2_rn(sum_c, sum_d));
+      const float sum = sum2.x + sum2.y;
       l += sum;
       tmem_st_32x32(s_tmem, packed0);       // keys 0..63  -> columns 0..31
       tmem_st_32x32(s_tmem + 32, packed1);  // keys 64..127 -> columns 32..63
