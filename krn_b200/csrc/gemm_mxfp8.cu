@@ -53,7 +53,12 @@ template <int CTA_GROUP, bool FP4>
 struct Layout {
   static constexpr int kBRows = kBN / CTA_GROUP;           // rows of B this CTA loads
   static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block (128 bytes per row): this CTA's A and B rows
-  static constexpr int kStageBytes = 2 * kBlockBytes;         // a stage = two K blocks behind ONE barrier
+  // A stage is two K blocks behind ONE barrier for MXFP8 (one poll and one commit of the issuing warp per 256 codes).
+  // NVFP4 has four times the scale bytes to keep in shared memory, and what its speed needs first is operand bytes in
+  // flight (with two 64 KB stages only one is ever being filled, and the TMA round trip then sets the K-block rate): its
+  // stages are single K blocks, five of them in a pair.
+  static constexpr int kBlocksPerStage = FP4 ? 1 : 2;
+  static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes;
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
   // four instructions take four bytes each.
   static constexpr int kScaleSets = FP4 ? 4 : 1;
@@ -65,7 +70,7 @@ struct Layout {
   // make room), two alone.
   static constexpr int kScaleChunk = FP4 ? (CTA_GROUP == 2 ? 4 : 2) : (CTA_GROUP == 2 ? 8 : 4);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-  static constexpr int kStages = (CTA_GROUP == 2 && !FP4) ? 3 : 2;
+  static constexpr int kStages = FP4 ? 4 : (CTA_GROUP == 2 ? 3 : 2);
   // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
   // cluster-scope arrive) does not fit behind one slot of four K blocks.
   static constexpr int kScaleSlots = (FP4 && CTA_GROUP == 2) ? 3 : 2;
@@ -169,6 +174,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   constexpr int kScaleSlotBytes = L::kScaleSlotBytes;
   constexpr int kScaleBlockBytes = L::kScaleBlockBytes;
   constexpr int kScaleSlots = L::kScaleSlots;
+  constexpr int kBlocksPerStage = L::kBlocksPerStage;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -202,7 +208,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int s = 0; s < kScaleSlots; ++s) {
-      mbar_init(scale_full_bar + 8 * s, 2 * CTA_GROUP);  // the two loader warps of every CTA of the tile
+      // MXFP8: both loader warps of every CTA of the tile fill each slot; NVFP4: one of them
+      mbar_init(scale_full_bar + 8 * s, (FP4 ? 1 : 2) * CTA_GROUP);
       mbar_init(scale_empty_bar + 8 * s, 1);             // the issuing thread's commit
     }
     mbar_init(tmem_full_bar, 1);
@@ -237,12 +244,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tile_coords(t, p, tm, tn);
         const int row_a = tm * (kBM * CTA_GROUP) + int(rank) * kBM;
         const int row_b = tn * kBN + int(rank) * L::kBRows;
-        for (int kb = 0; kb < num_kb; kb += 2) {
+        for (int kb = 0; kb < num_kb; kb += kBlocksPerStage) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kSiteProducerEmpty)) {
             ok = false;
             break;
           }
-          const int blocks = min(2, num_kb - kb);  // an odd K-block count leaves the last stage half full
+          const int blocks = min(kBlocksPerStage, num_kb - kb);  // an odd K-block count leaves the last stage half full
           const uint32_t dst = stages_addr + stage * kStageBytes;
           if constexpr (CTA_GROUP == 1) {
             mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * kBlockBytes);
@@ -289,13 +296,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // the single accumulator must have been read out by the epilogue of the previous tile
         if (!wait(tmem_empty_bar, (iter & 1u) ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after();
-        for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += kBlocksPerStage) {
           if (!wait(full_bar + 8 * stage, phase, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const int blocks = min(2, num_kb - kb0);
+          const int blocks = min(kBlocksPerStage, num_kb - kb0);
           for (int j = 0; j < blocks && ok; ++j) {
             const int kb = kb0 + j;
             const int in_chunk = kb & (kScaleChunk - 1);
@@ -375,53 +382,103 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // six per thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
     // group. Rows beyond the matrix get the code of 2^0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
-    uint32_t slot = 0, slot_phase = 0;
-    bool ok = true;
     const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
-    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
-      int tm, tn;
-      tile_coords(t, p, tm, tn);
-      for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk) {
-        const int blocks_here = min(kScaleChunk, num_kb - kb0);
-        // NVFP4: the 16-byte loads of the whole slot are issued before the wait for the slot, so that their latency
-        // runs beside the products still reading it (a slot is four K blocks only, there is four times the data)
-        uint4 early[FP4 ? 6 : 1][FP4 ? kScaleChunk : 1];
-        if constexpr (FP4) {
+    if constexpr (FP4) {
+      // NVFP4: 16 scale bytes per row and K block (word i belongs to the block's i-th instruction), 384 rows. Filling a
+      // slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive (about 1000) —
+      // that one warp cannot repeat every four K blocks (it was what the whole kernel waited for: 2000-2900 cycles
+      // of every 4100). So the two loader warps take alternate slots, each filling its own slot of the ring with all
+      // 384 rows (twelve per lane), and a slot is then due only every eight K blocks per warp; in a pair the ring has
+      // three slots, so that a warp may refill one slot while the issuing warp still has a whole slot in hand. Lane s of a 128-row
+      // group's pass takes row (s % 4) * 32 + s / 4, whose place in the tcgen05.cp layout is word s: a warp's stores
+      // fall on consecutive words.
+      const int mine = warp - 2;  // this warp fills every other slot of the ring
+      uint32_t slot = 0, slot_phase = 0;
+      int chunk_index = 0;
+      for (int t = first_tile; t < num_tiles; t += tile_step) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        bool ok = true;
+        for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk_index) {
+          if ((chunk_index & 1) != mine) {
+            if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
+            continue;
+          }
+          uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
+          const int blocks_here = min(kScaleChunk, num_kb - kb0);
+          uint4 v[12][kScaleChunk];
+#pragma unroll
+          for (int i = 0; i < 12; ++i) {
+            const int group = i >> 2;                      // 0: A rows, 1 / 2: B rows 0-127 / 128-255
+            const int s_index = (i & 3) * 32 + int(lane);
+            const int q = (s_index & 3) * 32 + (s_index >> 2);
+            const bool is_a = group == 0;
+            const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + q
+                                       : (long long)tn * kBN + (group - 1) * 128 + q;
+            const bool live = row < (is_a ? p.m : p.n);
+            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 16;
+#pragma unroll
+            for (int j = 0; j < kScaleChunk; ++j) {
+              // rows beyond the matrix (their codes are zero-filled by TMA) get the code of 1.0 (0x38)
+              v[i][j] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+              if (live && j < blocks_here) v[i][j] = __ldg(reinterpret_cast<const uint4*>(src) + j);
+            }
+          }
+          if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
+                                                 kSiteScaleEmpty))) {
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int i = 0; i < 12; ++i) {
+            uint8_t* dst = slot_base + (i >> 2) * 512 + ((i & 3) * 32 + int(lane)) * 4;
+#pragma unroll
+            for (int j = 0; j < kScaleChunk; ++j) {
+              uint8_t* block_dst = dst + j * kScaleBlockBytes;
+              *reinterpret_cast<uint32_t*>(block_dst) = v[i][j].x;
+              *reinterpret_cast<uint32_t*>(block_dst + kScaleGroupBytes) = v[i][j].y;
+              *reinterpret_cast<uint32_t*>(block_dst + 2 * kScaleGroupBytes) = v[i][j].z;
+              *reinterpret_cast<uint32_t*>(block_dst + 3 * kScaleGroupBytes) = v[i][j].w;
+            }
+          }
+          fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTA_GROUP == 2) {
+              mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
+            } else {
+              mbar_arrive(scale_full_bar + 8 * slot);
+            }
+          }
+          if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
+        }
+        if (!ok) break;
+      }
+    } else {
+      uint32_t slot = 0, slot_phase = 0;
+      bool ok = true;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk) {
+          const int blocks_here = min(kScaleChunk, num_kb - kb0);
+          if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
+                                                 kSiteScaleEmpty))) {
+            ok = false;
+            break;
+          }
+          uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
 #pragma unroll
           for (int i = 0; i < 6; ++i) {
-            const int r = tid + i * 64;
+            const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
             const bool is_a = r < kBM;
             const int local = is_a ? r : r - kBM;
             const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
                                        : (long long)tn * kBN + local;
             const bool live = row < (is_a ? p.m : p.n);
-            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 16;
-#pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) {
-              // rows beyond the matrix get the code of 1.0 (0x38)
-              early[i][j] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
-              if (live && j < blocks_here) early[i][j] = __ldg(reinterpret_cast<const uint4*>(src) + j);
-            }
-          }
-        }
-        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
-                                               kSiteScaleEmpty))) {
-          ok = false;
-          break;
-        }
-        uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-#pragma unroll
-        for (int i = 0; i < 6; ++i) {
-          const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
-          const bool is_a = r < kBM;
-          const int local = is_a ? r : r - kBM;
-          const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
-                                     : (long long)tn * kBN + local;
-          const bool live = row < (is_a ? p.m : p.n);
-          const int group = is_a ? 0 : 1 + local / 128;
-          const int in_group = local & 127;
-          uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
-          if constexpr (!FP4) {
+            const int group = is_a ? 0 : 1 + local / 128;
+            const int in_group = local & 127;
+            uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
             uint32_t w[kScaleChunk];
 #pragma unroll
             for (int j = 0; j < kScaleChunk; ++j) w[j] = 0x7f7f7f7fu;
@@ -439,29 +496,18 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
 #pragma unroll
             for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
-          } else {
-            // 16 scale bytes per row and K block: word i belongs to the block's i-th instruction
-#pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) {
-              const uint4 v = early[i][j];
-              uint8_t* block_dst = dst + j * kScaleBlockBytes;
-              *reinterpret_cast<uint32_t*>(block_dst) = v.x;
-              *reinterpret_cast<uint32_t*>(block_dst + kScaleGroupBytes) = v.y;
-              *reinterpret_cast<uint32_t*>(block_dst + 2 * kScaleGroupBytes) = v.z;
-              *reinterpret_cast<uint32_t*>(block_dst + 3 * kScaleGroupBytes) = v.w;
+          }
+          fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTA_GROUP == 2) {
+              mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
+            } else {
+              mbar_arrive(scale_full_bar + 8 * slot);
             }
           }
+          if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
         }
-        fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (CTA_GROUP == 2) {
-            mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
-          } else {
-            mbar_arrive(scale_full_bar + 8 * slot);
-          }
-        }
-        if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
       }
     }
   } else {
