@@ -562,7 +562,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         __syncwarp();
         if (lane == 0) {
           if constexpr (CTA_GROUP == 2) {
-            mbar_arrive_cluster(leader_tmem_empty);
+            // relaxed: the accumulator's values already sit in registers (tcgen05.wait::ld), nothing written by this
+            // thread has to be seen by the issuing thread, and a cluster-scope release costs about a thousand cycles
+            // of the one phase of a tile that nothing overlaps
+            mbar_arrive_cluster_relaxed(leader_tmem_empty);
           } else {
             mbar_arrive(tmem_empty_bar);
           }
@@ -594,10 +597,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
           tmem_ld_wait(lo, hi);
           if constexpr (FP4) {
+            const float2 alpha2 = make_float2(scales.alpha, scales.alpha);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              lo[i] = __float_as_uint(__uint_as_float(lo[i]) * scales.alpha);
-              hi[i] = __float_as_uint(__uint_as_float(hi[i]) * scales.alpha);
+            for (int i = 0; i < 16; ++i) {
+              const float2 l2 = __fmul2_rn(make_float2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1])), alpha2);
+              const float2 h2 = __fmul2_rn(make_float2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1])), alpha2);
+              lo[2 * i] = __float_as_uint(l2.x), lo[2 * i + 1] = __float_as_uint(l2.y);
+              hi[2 * i] = __float_as_uint(h2.x), hi[2 * i + 1] = __float_as_uint(h2.y);
             }
           }
 #pragma unroll
