@@ -16,10 +16,11 @@
 //   warp 1      MMA issuer: per K block of 128 codes, copies that block's scale factors from shared memory into tensor
 //               memory (tcgen05.cp, 32x128b.warpx4: one 512-byte group per 128 rows) and issues four K = 32
 //               instructions whose descriptors select the scale byte of their 32-wide sub-block
-//   warps 2-3   scale loaders: fetch, four K blocks at a time, the 16 scale bytes of this CTA's 128 A rows and of ALL 256
-//               B rows of the tile (each CTA of a pair multiplies its A rows by every column, so it needs every column's
-//               scale) and lay them out in shared memory the way tcgen05.cp expects a 128-row group:
-//               byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block. In a pair the leader's one tcgen05.cp
+//   warps 2-3   scale loaders: each warp fills every other slot of the scale ring (eight K blocks per slot in a pair) with
+//               the scale bytes of this CTA's 128 A rows and of ALL 256 B rows of the tile (each CTA of a pair multiplies
+//               its A rows by every column, so it needs every column's scale), laid out in shared memory the way
+//               tcgen05.cp expects a 128-row group: byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block. The loads
+//               of a slot are issued before the wait for the slot. In a pair the leader's one tcgen05.cp
 //               (cta_group::2) makes each CTA copy from its OWN shared memory into its own tensor memory
 //   warps 4-7   epilogue: tensor memory -> registers -> output type -> swizzled staging -> TMA store
 //
@@ -208,8 +209,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int s = 0; s < kScaleSlots; ++s) {
-      // MXFP8: both loader warps of every CTA of the tile fill each slot; NVFP4: one of them
-      mbar_init(scale_full_bar + 8 * s, (FP4 ? 1 : 2) * CTA_GROUP);
+      // one loader warp of every CTA of the tile fills a slot (both of them when the scale rows are only 4-byte aligned)
+      mbar_init(scale_full_bar + 8 * s, ((FP4 || scales.vector_ok) ? 1 : 2) * CTA_GROUP);
       mbar_init(scale_empty_bar + 8 * s, 1);             // the issuing thread's commit
     }
     mbar_init(tmem_full_bar, 1);
@@ -377,22 +378,24 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
     }
   } else if (warp < 4) {
-    // ---------------------------------------------------------------- scale loaders (64 threads)
-    // Per ring slot: the 16 scale bytes (four K blocks) of this CTA's 128 A rows and the tile's 256 B rows — 384 rows,
-    // six per thread, one 16-byte load each. Word j of a row goes to K block j of the slot, at the row's place in its 128-row
-    // group. Rows beyond the matrix get the code of 2^0 (their codes are zero-filled by TMA, the product stays zero).
+    // ---------------------------------------------------------------- scale loaders (two warps)
+    // Per ring slot: the scale bytes of this CTA's 128 A rows and the tile's 256 B rows, 384 rows. Rows beyond the matrix
+    // get the code of 1.0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
     const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
-    if constexpr (FP4) {
-      // NVFP4: 16 scale bytes per row and K block (word i belongs to the block's i-th instruction), 384 rows. Filling a
-      // slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive (about 1000) —
-      // that one warp cannot repeat every four K blocks (it was what the whole kernel waited for: 2000-2900 cycles
-      // of every 4100). So the two loader warps take alternate slots, each filling its own slot of the ring with all
-      // 384 rows (twelve per lane), and a slot is then due only every eight K blocks per warp; in a pair the ring has
-      // three slots, so that a warp may refill one slot while the issuing warp still has a whole slot in hand. Lane s of a 128-row
-      // group's pass takes row (s % 4) * 32 + s / 4, whose place in the tcgen05.cp layout is word s: a warp's stores
-      // fall on consecutive words.
-      const int mine = warp - 2;  // this warp fills every other slot of the ring
+    if (FP4 || scales.vector_ok) {
+      // Filling a ring slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive
+      // (about 1000) — and a trace of the issuing warp showed it waiting for scale factors 2000-2900 cycles of every
+      // slot when both loader warps worked on every slot one after the other. So the two loader warps take ALTERNATE
+      // slots, each filling its slot with all 384 rows (twelve per lane), and they issue the loads before they wait for
+      // the slot: a slot then costs a warp max(load latency, wait) + stores + arrive once per two slots.
+      // A row's bytes for one slot are contiguous: word k belongs to K block k of the slot (MXFP8: one word = the four
+      // 32-wide sub-blocks of a K block) or to instruction k % 4 of K block k / 4 (NVFP4: one word = the four 16-wide
+      // blocks of a 64-code instruction). Lane s of a 128-row group's pass takes row (s % 4) * 32 + s / 4, whose place in
+      // the tcgen05.cp layout is word s: a warp's stores fall on consecutive words.
+      constexpr int kWords = kScaleChunk * (FP4 ? 4 : 1);  // 32-bit words of scale bytes per row and slot
+      constexpr uint32_t kUnit = FP4 ? 0x38383838u : 0x7f7f7f7fu;  // the code of 1.0, for rows beyond the matrix
+      const int mine = warp - 2;
       uint32_t slot = 0, slot_phase = 0;
       int chunk_index = 0;
       for (int t = first_tile; t < num_tiles; t += tile_step) {
@@ -405,8 +408,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             continue;
           }
           uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-          const int blocks_here = min(kScaleChunk, num_kb - kb0);
-          uint4 v[12][kScaleChunk];
+          const int words_here = min(kScaleChunk, num_kb - kb0) * (FP4 ? 4 : 1);
+          uint32_t w[12][kWords];
 #pragma unroll
           for (int i = 0; i < 12; ++i) {
             const int group = i >> 2;                      // 0: A rows, 1 / 2: B rows 0-127 / 128-255
@@ -416,12 +419,23 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + q
                                        : (long long)tn * kBN + (group - 1) * 128 + q;
             const bool live = row < (is_a ? p.m : p.n);
-            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 16;
+            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) +
+                                 (long long)kb0 * (FP4 ? 16 : 4);
 #pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) {
-              // rows beyond the matrix (their codes are zero-filled by TMA) get the code of 1.0 (0x38)
-              v[i][j] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
-              if (live && j < blocks_here) v[i][j] = __ldg(reinterpret_cast<const uint4*>(src) + j);
+            for (int k = 0; k < kWords; ++k) w[i][k] = kUnit;
+            if (live) {
+#pragma unroll
+              for (int v = 0; v < kWords / 4; ++v) {
+                if (4 * v + 4 <= words_here) {
+                  const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
+                  w[i][4 * v] = x.x, w[i][4 * v + 1] = x.y, w[i][4 * v + 2] = x.z, w[i][4 * v + 3] = x.w;
+                } else {
+                  // the row ends inside this vector (MXFP8 with a K-block count that is not a multiple of four)
+#pragma unroll
+                  for (int k = 4 * v; k < 4 * v + 4; ++k)
+                    if (k < words_here) w[i][k] = __ldg(reinterpret_cast<const uint32_t*>(src) + k);
+                }
+              }
             }
           }
           if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
@@ -433,12 +447,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           for (int i = 0; i < 12; ++i) {
             uint8_t* dst = slot_base + (i >> 2) * 512 + ((i & 3) * 32 + int(lane)) * 4;
 #pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) {
-              uint8_t* block_dst = dst + j * kScaleBlockBytes;
-              *reinterpret_cast<uint32_t*>(block_dst) = v[i][j].x;
-              *reinterpret_cast<uint32_t*>(block_dst + kScaleGroupBytes) = v[i][j].y;
-              *reinterpret_cast<uint32_t*>(block_dst + 2 * kScaleGroupBytes) = v[i][j].z;
-              *reinterpret_cast<uint32_t*>(block_dst + 3 * kScaleGroupBytes) = v[i][j].w;
+            for (int k = 0; k < kWords; ++k) {
+              const int block = FP4 ? k / 4 : k, set = FP4 ? k % 4 : 0;
+              *reinterpret_cast<uint32_t*>(dst + block * kScaleBlockBytes + set * kScaleGroupBytes) = w[i][k];
             }
           }
           fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
@@ -455,6 +466,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (!ok) break;
       }
     } else {
+      // MXFP8 scale rows that are only 4-byte aligned: both warps fill every slot with word loads
       uint32_t slot = 0, slot_phase = 0;
       bool ok = true;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
