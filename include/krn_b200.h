@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8, krn_b200_gemm_mxfp8_tn and krn_b200_gemm_nvfp4_tn added */
+#define KRN_B200_ABI_VERSION 2 /* 2: the paged decode entries take num_pages, the gather entries sync words; krn_b200_gemm_fp8, krn_b200_gemm_mxfp8_tn, krn_b200_gemm_nvfp4_tn and krn_b200_gemm_mxfp4_tn added */
 
 /* status codes */
 #define KRN_B200_OK 0
@@ -176,6 +176,20 @@ int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* sa, const v
  *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
 int krn_b200_gemm_nvfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, float alpha, void* c,
                            int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
+                           void* stream);
+
+/* C[M,N] = sum over 32-wide K blocks kb of  2^(sa[m,kb] - 127) * 2^(sb[n,kb] - 127) * (A4[m, kb] . B4[n, kb]): the product
+ * of two matrices in the reference's MXFP4 block format — e2m1 codes packed two per byte (low nibble first), one e8m0
+ * scale byte per 1 x 32 block of a row (src/krn/data/formats.py:129-135; `QMatrix[MXFP4]`, whose `@` the reference
+ * declares and does not implement). tcgen05.mma kind::mxf4.block_scale.scale_vec::2X.
+ *   a, b    packed e2m1 codes, K-major: a [M, K / 2] bytes, b [N, K / 2] bytes; lda / ldb row pitches in BYTES,
+ *           multiples of 16
+ *   sa, sb  e8m0 bytes: sa [M, K / 32], sb [N, K / 32]; ldsa / ldsb row pitches in bytes; addresses and pitches
+ *           multiples of 16
+ *   K       the number of codes per row, a multiple of 512; M, N ragged as in krn_b200_gemm_tn
+ *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
+int krn_b200_gemm_mxfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c, int64_t m,
+                           int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa, int64_t ldsb,
                            void* stream);
 
 /* The block-scaled FP8 product sharded by output columns with the all-gather of the columns done by the kernel's

@@ -50,8 +50,15 @@ constexpr int kThreads = 256;
 constexpr int kABytes = kBM * 128;
 constexpr int kScaleGroupBytes = 512 + 2 * 512;         // one set of scale copies: the A group, then two B groups of 128 rows
 constexpr int kEpilogueBytes = 4 * 2048;                // per epilogue warp: one 16-row x 128-byte store box
-template <int CTA_GROUP, bool FP4>
+constexpr int kMxfp8 = 0, kNvfp4 = 1, kMxfp4 = 2;  // FORMAT: what the codes and the scale bytes are
+
+template <int CTA_GROUP, int FORMAT>
 struct Layout {
+  static constexpr bool FP4 = FORMAT != kMxfp8;            // 4-bit codes, 256 per 128-byte stage row
+  // 32-bit words of scale bytes per row and K block = sets of scale copies per K block: MXFP8 one (a byte per 32 codes,
+  // its four instructions pick their byte of the one column), NVFP4 four (a byte per 16 codes: every 64-code
+  // instruction takes a whole word), MXFP4 two (a byte per 32 codes: two instructions share a word).
+  static constexpr int kWordsPerBlock = FORMAT == kNvfp4 ? 4 : FORMAT == kMxfp4 ? 2 : 1;
   static constexpr int kBRows = kBN / CTA_GROUP;           // rows of B this CTA loads
   static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block (128 bytes per row): this CTA's A and B rows
   // A stage is two K blocks behind ONE barrier for MXFP8 (one poll and one commit of the issuing warp per 256 codes).
@@ -62,14 +69,14 @@ struct Layout {
   static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes;
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
   // four instructions take four bytes each.
-  static constexpr int kScaleSets = FP4 ? 4 : 1;
+  static constexpr int kScaleSets = kWordsPerBlock;
   static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes;
   // K blocks of scales per ring slot. An MXFP8 pair takes eight (32 scale bytes per row): the peer's loaders signal the
   // leader with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide
   // that together with the global-memory latency behind the K blocks of the other slot; four were measured 17 %
   // slower. NVFP4 has four times the scale bytes: four K blocks per slot in a pair (with one operand stage fewer to
   // make room), two alone.
-  static constexpr int kScaleChunk = FP4 ? (CTA_GROUP == 2 ? 4 : 2) : (CTA_GROUP == 2 ? 8 : 4);
+  static constexpr int kScaleChunk = (CTA_GROUP == 2 ? 8 : 4) / (FORMAT == kNvfp4 ? 2 : 1);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
   static constexpr int kStages = FP4 ? 4 : (CTA_GROUP == 2 ? 3 : 2);
   // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
@@ -80,8 +87,9 @@ struct Layout {
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
 constexpr int kTmemScaleB = 260;                        // and 8 of B; sets are 12 columns apart
-static_assert(Layout<1, false>::kSmemBytes <= 232448 && Layout<2, false>::kSmemBytes <= 232448 &&
-              Layout<1, true>::kSmemBytes <= 232448 && Layout<2, true>::kSmemBytes <= 232448, "shared memory budget");
+static_assert(Layout<1, kMxfp8>::kSmemBytes <= 232448 && Layout<2, kMxfp8>::kSmemBytes <= 232448 &&
+              Layout<1, kNvfp4>::kSmemBytes <= 232448 && Layout<2, kNvfp4>::kSmemBytes <= 232448 &&
+              Layout<1, kMxfp4>::kSmemBytes <= 232448 && Layout<2, kMxfp4>::kSmemBytes <= 232448, "shared memory budget");
 
 struct MxScales {
   const uint8_t* sa;  // [M, K / 32] e8m0, or [M, K / 16] e4m3 for NVFP4
@@ -127,6 +135,30 @@ __device__ __forceinline__ void umma_nvf4(uint32_t d_tmem, uint32_t a_lo, uint32
   }
 }
 
+// Instruction descriptor of kind::mxf4.block_scale.scale_vec::2X (MXFP4): e2m1 operands, e8m0 scales (bit 23), and
+// the scale id picks which half (bytes 0-1 or 2-3) of a scale-factor column belongs to this 64-code instruction.
+__device__ __forceinline__ uint32_t mxf4_idesc(uint32_t scale_id, uint32_t m) {
+  return (scale_id << 4) | (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (scale_id << 29);
+}
+
+template <int CTA_GROUP>
+__device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                          uint32_t scale_a_tmem, uint32_t scale_b_tmem, uint32_t accumulate) {
+  if constexpr (CTA_GROUP == 1) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %4, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate)
+        : "memory");
+  }
+}
+
 // D[tmem] (+)= (A * scale_a) * (B * scale_b): A, B shared-memory descriptors, scales in tensor memory. One thread.
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
@@ -161,13 +193,15 @@ __device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t sm
   }
 }
 
-template <int CTA_GROUP, bool FP4, typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, Problem p, MxScales scales, DeviceStatus* status) {
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
-  using L = Layout<CTA_GROUP, FP4>;
+  using L = Layout<CTA_GROUP, FORMAT>;
+  constexpr bool FP4 = L::FP4;
+  constexpr int kWordsPerBlock = L::kWordsPerBlock;
   constexpr int kStages = L::kStages;
   constexpr int kStageBytes = L::kStageBytes;
   constexpr int kBlockBytes = L::kBlockBytes;
@@ -328,7 +362,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
                                      tmem_base + kTmemScaleA, tmem_base + kTmemScaleB, (kb > 0 || ks > 0) ? 1u : 0u);
                 }
-              } else {
+              } else if constexpr (FORMAT == kNvfp4) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                   // each 64-code instruction has its own scale bytes, in its own tensor-memory columns
@@ -339,6 +373,20 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   scales_to_tmem<CTA_GROUP>(sfb + 4, set + 1024);
                   umma_nvf4<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, nvf4_idesc(kBM * CTA_GROUP), sfa, sfb,
                                        (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+              } else {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  // MXFP4: two 64-code instructions share a set of scale columns; each takes two of the four bytes
+                  const uint32_t sfa = tmem_base + kTmemScaleA + 12 * (ks >> 1), sfb = tmem_base + kTmemScaleB + 12 * (ks >> 1);
+                  if ((ks & 1) == 0) {
+                    const uint32_t set = block + (ks >> 1) * kScaleGroupBytes;
+                    scales_to_tmem<CTA_GROUP>(sfa, set);
+                    scales_to_tmem<CTA_GROUP>(sfb, set + 512);
+                    scales_to_tmem<CTA_GROUP>(sfb + 4, set + 1024);
+                  }
+                  umma_mxf4<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mxf4_idesc((ks & 1) * 2, kBM * CTA_GROUP), sfa,
+                                       sfb, (kb > 0 || ks > 0) ? 1u : 0u);
                 }
               }
               if (slot_done) {
@@ -393,8 +441,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       // 32-wide sub-blocks of a K block) or to instruction k % 4 of K block k / 4 (NVFP4: one word = the four 16-wide
       // blocks of a 64-code instruction). Lane s of a 128-row group's pass takes row (s % 4) * 32 + s / 4, whose place in
       // the tcgen05.cp layout is word s: a warp's stores fall on consecutive words.
-      constexpr int kWords = kScaleChunk * (FP4 ? 4 : 1);  // 32-bit words of scale bytes per row and slot
-      constexpr uint32_t kUnit = FP4 ? 0x38383838u : 0x7f7f7f7fu;  // the code of 1.0, for rows beyond the matrix
+      constexpr int kWords = kScaleChunk * kWordsPerBlock;  // 32-bit words of scale bytes per row and slot
+      constexpr uint32_t kUnit = FORMAT == kNvfp4 ? 0x38383838u : 0x7f7f7f7fu;  // the code of 1.0 (e4m3 / e8m0), for rows beyond the matrix
       const int mine = warp - 2;
       uint32_t slot = 0, slot_phase = 0;
       int chunk_index = 0;
@@ -408,7 +456,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             continue;
           }
           uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-          const int words_here = min(kScaleChunk, num_kb - kb0) * (FP4 ? 4 : 1);
+          const int words_here = min(kScaleChunk, num_kb - kb0) * kWordsPerBlock;
           uint32_t w[12][kWords];
 #pragma unroll
           for (int i = 0; i < 12; ++i) {
@@ -420,7 +468,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                        : (long long)tn * kBN + (group - 1) * 128 + q;
             const bool live = row < (is_a ? p.m : p.n);
             const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) +
-                                 (long long)kb0 * (FP4 ? 16 : 4);
+                                 (long long)kb0 * (4 * kWordsPerBlock);
 #pragma unroll
             for (int k = 0; k < kWords; ++k) w[i][k] = kUnit;
             if (live) {
@@ -448,7 +496,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint8_t* dst = slot_base + (i >> 2) * 512 + ((i & 3) * 32 + int(lane)) * 4;
 #pragma unroll
             for (int k = 0; k < kWords; ++k) {
-              const int block = FP4 ? k / 4 : k, set = FP4 ? k % 4 : 0;
+              const int block = k / kWordsPerBlock, set = k % kWordsPerBlock;
               *reinterpret_cast<uint32_t*>(dst + block * kScaleBlockBytes + set * kScaleGroupBytes) = w[i][k];
             }
           }
@@ -590,7 +638,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           uint32_t words[32];
           tmem_ld_32x32(t_row + chunk * kChunkCols, words);
           tmem_ld_wait(words);
-          if constexpr (FP4) {
+          if constexpr (FORMAT == kNvfp4) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) words[i] = __float_as_uint(__uint_as_float(words[i]) * scales.alpha);
           }
@@ -608,7 +656,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tmem_ld_32x32(t_row + chunk * kChunkCols, lo);
           tmem_ld_32x32(t_row + chunk * kChunkCols + 32, hi);
           tmem_ld_wait(lo, hi);
-          if constexpr (FP4) {
+          if constexpr (FORMAT == kNvfp4) {
             const float2 alpha2 = make_float2(scales.alpha, scales.alpha);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -654,11 +702,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
-template <int CTA_GROUP, bool FP4, typename OutT, bool OUT_BF16>
+template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
            MxScales scales, cudaStream_t stream) {
-  using L = Layout<CTA_GROUP, FP4>;
-  auto kernel = gemm_mxfp8_kernel<CTA_GROUP, FP4, OutT, OUT_BF16>;
+  using L = Layout<CTA_GROUP, FORMAT>;
+  auto kernel = gemm_mxfp8_kernel<CTA_GROUP, FORMAT, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / CTA_GROUP;
@@ -679,20 +727,21 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   return KRN_B200_OK;
 }
 
-template <int CTA_GROUP, bool FP4>
+template <int CTA_GROUP, int FORMAT>
 int launch_for_output(const DeviceContext* ctx, int c_type, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                       Problem p, MxScales scales, cudaStream_t stream) {
-  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FP4, float, false>(ctx, ma, mb, mc, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FP4, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
-  return launch<CTA_GROUP, FP4, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
+  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FORMAT, float, false>(ctx, ma, mb, mc, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FORMAT, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
+  return launch<CTA_GROUP, FORMAT, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
 }
 
 // Checks shared by the two entry points, the tensor maps (operand rows as bytes: 128 per K block) and the launch.
 // `k_bytes` is the length of an operand row in bytes, `scale_bytes` of a scale row.
-template <bool FP4>
+template <int FORMAT>
 int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, float alpha, void* c,
                          int64_t m, int64_t n, int64_t k_bytes, int64_t scale_bytes, int64_t lda, int64_t ldb, int64_t ldc,
                          int64_t ldsa, int64_t ldsb, cudaStream_t stream) {
+  constexpr bool FP4 = FORMAT != kMxfp8;
   const int c_bytes = c_type == KRN_B200_F32 ? 4 : 2;
   if (ldc < n || lda < k_bytes || ldb < k_bytes || ldsa < scale_bytes || ldsb < scale_bytes) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "row pitch shorter than the row");
@@ -702,8 +751,8 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   }
   const bool vector_ok = aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0;
   if (FP4 && !vector_ok) {
-    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "NVFP4 scale matrices need 16-byte aligned addresses and row pitches (the 16 "
-                "scale bytes of a 256-code K step are fetched as one vector)");
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the scale matrices of a 4-bit product need 16-byte aligned addresses and row pitches "
+                "(a row's scale bytes are fetched as 16-byte vectors)");
   }
   if (!FP4 && (reinterpret_cast<uintptr_t>(sa) % 4 != 0 || reinterpret_cast<uintptr_t>(sb) % 4 != 0 || ldsa % 4 != 0 ||
                ldsb % 4 != 0)) {
@@ -746,8 +795,8 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  if (group == 2) return launch_for_output<2, FP4>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
-  return launch_for_output<1, FP4>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  if (group == 2) return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
 }
 
 }  // namespace
@@ -773,7 +822,7 @@ extern "C" int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* 
   if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
-  return block_scaled_product<false>(c_type, a, sa, b, sb, 1.0f, c, m, n, k, k / 32, lda, ldb, ldc, ldsa, ldsb, stream);
+  return block_scaled_product<kMxfp8>(c_type, a, sa, b, sb, 1.0f, c, m, n, k, k / 32, lda, ldb, ldc, ldsa, ldsb, stream);
 }
 
 extern "C" int krn_b200_gemm_nvfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb,
@@ -797,5 +846,29 @@ extern "C" int krn_b200_gemm_nvfp4_tn(int c_type, const void* a, const uint8_t* 
   if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
   }
-  return block_scaled_product<true>(c_type, a, sa, b, sb, alpha, c, m, n, k / 2, k / 16, lda, ldb, ldc, ldsa, ldsb, stream);
+  return block_scaled_product<kNvfp4>(c_type, a, sa, b, sb, alpha, c, m, n, k / 2, k / 16, lda, ldb, ldc, ldsa, ldsb, stream);
+}
+
+extern "C" int krn_b200_gemm_mxfp4_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c,
+                                      int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa,
+                                      int64_t ldsb, void* stream_handle) {
+  using namespace krnb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (c_type != KRN_B200_BF16 && c_type != KRN_B200_F16 && c_type != KRN_B200_F32) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "output type %d is not available: use bf16, f16 or f32", c_type);
+  }
+  if (m < 0 || n < 0 || k < 0) return fail(KRN_B200_ERR_INVALID_ARGUMENT, "negative extent");
+  if (m == 0 || n == 0) return KRN_B200_OK;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "extents beyond 2^31-1 are not supported");
+  }
+  if (k == 0 || k % 512 != 0) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "MXFP4 product with K = %lld is not available on sm_100a: the kernel consumes 256 "
+                "codes per step and fetches the scale bytes of two steps as one 16-byte vector. Instead: pad K to a multiple "
+                "of 512 with zero codes", (long long)k);
+  }
+  if (a == nullptr || b == nullptr || c == nullptr || sa == nullptr || sb == nullptr) {
+    return fail(KRN_B200_ERR_INVALID_ARGUMENT, "null tensor address");
+  }
+  return block_scaled_product<kMxfp4>(c_type, a, sa, b, sb, 1.0f, c, m, n, k / 2, k / 32, lda, ldb, ldc, ldsa, ldsb, stream);
 }

@@ -37,9 +37,9 @@ def matmul(a: Any, b: Any, out: Any, stream: Any = None) -> Any:
 class QMatrix:
     """A block-scaled matrix on the device, with the fields of the reference's `QMatrix[F]` struct
     (src/krn/frontend/memory.py:255-269): the block format `fmt` (a `krn_b200.formats.BlockFormat`: `FP8FN()`,
-    `FP8FNWeights()`, `MXFP8()` or `NVFP4()`), the logical `shape`, the `codes` ((rows, K), K contiguous — blocks run
-    along the contraction axis; one byte per element, or for NVFP4 two 4-bit codes per byte, low nibble first), the
-    `scales` (f32 for the FP8FN formats, e8m0 bytes for MXFP8, e4m3 bytes for NVFP4; one per block) and the per-tensor
+    `FP8FNWeights()`, `MXFP8()`, `MXFP4()` or `NVFP4()`), the logical `shape`, the `codes` ((rows, K), K contiguous — blocks run
+    along the contraction axis; one byte per element, or for the 4-bit formats two codes per byte, low nibble first), the
+    `scales` (f32 for the FP8FN formats, e8m0 bytes for MXFP8 and MXFP4, e4m3 bytes for NVFP4; one per block) and the per-tensor
     `tensor_scale` of formats that define one (NVFP4: a float)."""
 
     fmt: Any
@@ -99,6 +99,23 @@ def quantize_nvfp4_host(values: np.ndarray) -> tuple[np.ndarray, np.ndarray, flo
     return np.ascontiguousarray(packed), np.ascontiguousarray(scale_codes), float(tensor_scale)
 
 
+def quantize_mxfp4_host(values: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """(packed codes (rows, K / 2), e8m0 scale bytes (rows, K / 32)) of a float32 host matrix in the MXFP4 format
+    (src/krn/data/formats.py:129-135), by the OCP MX floor rule the format names: scale = 2^(floor(log2 absmax) - 2), 2
+    being the exponent of the largest e2m1 value; codes = e2m1(x / scale), two per byte, low nibble first."""
+    values = np.ascontiguousarray(values, np.float32)
+    rows, cols = values.shape
+    if cols % 32:
+        raise ValueError(f"cannot quantize a {rows} x {cols} matrix to mxfp4: rows must be whole 1 x 32 blocks")
+    blocks = values.reshape(rows, cols // 32, 32)
+    absmax = np.abs(blocks).max(axis=2)
+    exponent = np.where(absmax > 0, np.floor(np.log2(np.where(absmax > 0, absmax, 1.0))) - 2, 0)
+    exponent = np.clip(exponent, -127, 127).astype(np.int32)
+    codes = _e2m1_codes(blocks * np.exp2(-exponent.astype(np.float32))[:, :, None]).reshape(rows, cols)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    return np.ascontiguousarray(packed), np.ascontiguousarray((exponent + 127).astype(np.uint8))
+
+
 def quantize_host(values: np.ndarray, fmt: Any) -> tuple[np.ndarray, np.ndarray]:
     """(codes, scales) of a float32 host matrix (rows, K) in block format `fmt`, on the host.
 
@@ -137,6 +154,9 @@ def quantize(values: np.ndarray, fmt: Any, device: Any = None) -> QMatrix:
     if isinstance(fmt, formats.NVFP4):
         packed, scale_codes, tensor_scale = quantize_nvfp4_host(values)
         return QMatrix(fmt, tuple(values.shape), device.to_device(packed), device.to_device(scale_codes), tensor_scale)
+    if isinstance(fmt, formats.MXFP4):
+        packed, scale_codes = quantize_mxfp4_host(values)
+        return QMatrix(fmt, tuple(values.shape), device.to_device(packed), device.to_device(scale_codes))
     codes, stored = quantize_host(values, fmt)
     return QMatrix(fmt, tuple(values.shape), device.to_device(codes, f8e4m3fn), device.to_device(stored))
 
@@ -145,13 +165,16 @@ def matmul_q(a: QMatrix, b: QMatrix, out: Any, stream: Any = None) -> Any:
     """out[M, N] = a @ b^T for two block-scaled matrices whose blocks run along K (both stored (rows, K)) — the product
     the reference declares as `QTile.__matmul__` (src/krn/frontend/memory.py:173-193). Three pairings have kernels:
     FP8FN activations (1 x 128 f32 scales) with FP8FNWeights (128 x 128 f32 scales), whose partial sums are scaled as they
-    are accumulated, and MXFP8 with MXFP8 and NVFP4 with NVFP4, whose block scales the tensor cores apply themselves."""
+    are accumulated, and MXFP8 with MXFP8, MXFP4 with MXFP4 and NVFP4 with NVFP4, whose block scales the tensor cores apply
+    themselves."""
     from krn_b200 import formats
 
     if a.shape[1] != b.shape[1]:
         raise ValueError(f"contraction lengths differ: {a.shape} @ {b.shape}^T")
     if isinstance(a.fmt, formats.MXFP8) and isinstance(b.fmt, formats.MXFP8):
         calls.gemm_mxfp8_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
+    elif isinstance(a.fmt, formats.MXFP4) and isinstance(b.fmt, formats.MXFP4):
+        calls.gemm_mxfp4_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
     elif isinstance(a.fmt, formats.NVFP4) and isinstance(b.fmt, formats.NVFP4):
         alpha = float(a.tensor_scale if a.tensor_scale is not None else 1.0) * float(
             b.tensor_scale if b.tensor_scale is not None else 1.0)
@@ -160,7 +183,7 @@ def matmul_q(a: QMatrix, b: QMatrix, out: Any, stream: Any = None) -> Any:
         calls.gemm_fp8_blockscaled_tn(_raw(a.codes), _raw(a.scales), _raw(b.codes), _raw(b.scales), _raw(out), _stream(stream))
     else:
         raise TargetError(f"the product {a.fmt.name} @ {b.fmt.name}", "sm_100a", "no prebuilt kernel multiplies this pair "
-                          "of block formats", "use FP8FN activations with FP8FNWeights, MXFP8 with MXFP8, or NVFP4 with NVFP4")
+                          "of block formats", "use FP8FN activations with FP8FNWeights, MXFP8 with MXFP8, MXFP4 with MXFP4, or NVFP4 with NVFP4")
     return out
 
 

@@ -165,6 +165,24 @@ def gemm_mxfp8_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: Any = None) 
     native.check(status, "MXFP8 tile matrix product")
 
 
+def gemm_mxfp4_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, stream: Any = None) -> None:
+    """c = sum over 32-wide K blocks of 2^(sa - 127) * 2^(sb - 127) * (a4 @ b4^T): a [M, K/2], b [N, K/2] bytes of packed e2m1
+    codes (low nibble first), sa [M, K/32] and sb [N, K/32] e8m0 bytes (uint8). The tensor cores apply the scales."""
+    (m, k_bytes), (n, kb_bytes) = a.shape, b.shape
+    k = 2 * k_bytes
+    if kb_bytes != k_bytes or tuple(c.shape) != (m, n):
+        raise ValueError(f"shapes do not compose: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    if tuple(sa.shape) != (m, k // 32) or tuple(sb.shape) != (n, k // 32) or k % 32:
+        raise ValueError(f"scale shapes {tuple(sa.shape)}, {tuple(sb.shape)} do not match 1x32 blocks of K = {k}")
+    for t in (a, b, sa, sb):
+        if "uint8" not in str(t.dtype):
+            raise TypeError("MXFP4 codes and scales are bytes: pass uint8 tensors")
+    status = native.library().krn_b200_gemm_mxfp4_tn(
+        _type_of(c), _pointer(a), _pointer(sa), _pointer(b), _pointer(sb), _pointer(c), m, n, k, _pitch(a), _pitch(b),
+        _pitch(c), _pitch(sa), _pitch(sb), _stream(stream))
+    native.check(status, "MXFP4 tile matrix product")
+
+
 def gemm_nvfp4_tn(a: Any, sa: Any, b: Any, sb: Any, c: Any, alpha: float = 1.0, stream: Any = None) -> None:
     """c = alpha * sum over 16-wide K blocks of sa * sb * (a4 @ b4^T): a [M, K/2], b [N, K/2] bytes of packed e2m1 codes (low
     nibble first), sa [M, K/16] and sb [N, K/16] e4m3 bytes (uint8), alpha the product of the two tensor scales. The

@@ -35,6 +35,8 @@ PROTOTYPES: dict[str, tuple[type, list[type]]] = {
         _int, [_int, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_mxfp8_tn": (
         _int, [_int, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "krn_b200_gemm_mxfp4_tn": (
+        _int, [_int, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_nvfp4_tn": (
         _int, [_int, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "krn_b200_gemm_fp8_blockscaled_tn_gather": (

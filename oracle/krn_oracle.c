@@ -386,6 +386,42 @@ void krn_oracle_gemm_nvfp4(int c_type, const uint8_t* a, const uint8_t* sa, cons
   free(total);
 }
 
+/* MXFP4 product (src/krn/data/formats.py:129-135): C[i,j] = sum over 32-wide K blocks kb of (2^(sa[i,kb]-127) *
+ * 2^(sb[j,kb]-127)) * P_kb[i,j], a and b as in krn_oracle_gemm_nvfp4 (two e2m1 codes per byte, lower k in the low
+ * nibble), the scaled partials added in kb order in f32. Rows [row_begin, row_end). lda / ldb in bytes. */
+void krn_oracle_gemm_mxfp4(int c_type, const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb, void* c,
+                           int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldsa,
+                           int64_t ldsb, int64_t row_begin, int64_t row_end) {
+  (void)m;
+  float* bt = aligned_alloc(64, ((size_t)(k > 0 ? k : 1) * n * 4 + 63) / 64 * 64);
+  float* part = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  float* total = aligned_alloc(64, ((size_t)n * 4 + 63) / 64 * 64);
+  for (int64_t kk = 0; kk < k; ++kk)
+    for (int64_t j = 0; j < n; ++j) bt[kk * n + j] = krn_oracle_e2m1_decode((uint8_t)((b[j * ldb + kk / 2] >> (4 * (kk & 1))) & 15));
+  for (int64_t i = row_begin; i < row_end; ++i) {
+    for (int64_t j = 0; j < n; ++j) total[j] = 0.0f;
+    for (int64_t k0 = 0, kb = 0; k0 < k; k0 += 32, ++kb) {
+      int64_t k1 = k0 + 32 < k ? k0 + 32 : k;
+      for (int64_t j = 0; j < n; ++j) part[j] = 0.0f;
+      for (int64_t kk = k0; kk < k1; ++kk) {
+        float av = krn_oracle_e2m1_decode((uint8_t)((a[i * lda + kk / 2] >> (4 * (kk & 1))) & 15));
+        const float* brow = bt + kk * n;
+        for (int64_t j = 0; j < n; ++j) part[j] = __builtin_fmaf(av, brow[j], part[j]);
+      }
+      float sai = krn_oracle_e8m0_decode(sa[i * ldsa + kb]);
+      for (int64_t j = 0; j < n; ++j) {
+        float scale = sai * krn_oracle_e8m0_decode(sb[j * ldsb + kb]);
+        float scaled = scale * part[j];
+        total[j] = total[j] + scaled;
+      }
+    }
+    for (int64_t j = 0; j < n; ++j) store_from_f32(c, c_type, i * ldc + j, total[j]);
+  }
+  free(bt);
+  free(part);
+  free(total);
+}
+
 /* ---- flash attention, statement by statement --------------------------------------------------------- */
 
 static inline float krn_max(float a, float b) { return (a > b || a != a) ? a : b; } /* emit.py:116-120 */

@@ -52,6 +52,7 @@ def lib() -> ctypes.CDLL:
         handle.krn_oracle_gemm_fast.argtypes = [i32, i32, i32, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_fp8_blockscaled.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_mxfp8.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
+        handle.krn_oracle_gemm_mxfp4.argtypes = [i32, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64]
         handle.krn_oracle_gemm_nvfp4.argtypes = [i32, ptr, ptr, ptr, ptr, ctypes.c_float, ptr, i64, i64, i64, i64, i64, i64, i64,
                                                  i64, i64, i64]
         handle.krn_oracle_flash_attention.argtypes = [i32, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i32, f32, i32, i32, i32, i64, i64]
@@ -60,7 +61,7 @@ def lib() -> ctypes.CDLL:
         handle.krn_oracle_e4m3_decode_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_bf16_round_array.argtypes = [ptr, ptr, i64]
         handle.krn_oracle_matmul_epilogue.argtypes = [i32, ptr, ptr, ptr, i64, i64, i32]
-        for name in ("gemm_mxfp8", "gemm_nvfp4", "matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
+        for name in ("gemm_mxfp8", "gemm_nvfp4", "gemm_mxfp4", "matmul_epilogue", "gemm_blocks", "gemm_fast", "gemm_fp8_blockscaled", "flash_attention", "decode_fp8_paged",
                      "e4m3_encode_array", "e4m3_decode_array", "bf16_round_array"):
             getattr(handle, f"krn_oracle_{name}").restype = None
         _LIB = handle
@@ -265,6 +266,39 @@ def nvfp4_values(packed: np.ndarray, scales: np.ndarray, tensor_scale: float) ->
     """float64 values of an NVFP4 matrix."""
     values = e2m1_decode(unpack_nibbles(packed)).astype(np.float64)
     return values * np.repeat(e4m3_decode(scales).astype(np.float64), 16, axis=1) * float(tensor_scale)
+
+
+def quantize_mxfp4(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """(packed e2m1 codes, e8m0 scale bytes per 1 x 32 block) of the reference's MXFP4 format
+    (src/krn/data/formats.py:129-135) by the OCP MX floor rule: scale = 2^(floor(log2 amax) - 2), 2 being the exponent of
+    the largest e2m1 value (6 = 1.5 * 2^2); elements are x / scale rounded to e2m1, saturating. A block of zeros gets 2^0."""
+    rows, cols = x.shape
+    if cols % 32:
+        raise ValueError("the row length must be a multiple of 32")
+    blocks = np.ascontiguousarray(x, np.float32).reshape(rows, cols // 32, 32)
+    amax = np.abs(blocks).max(axis=2)
+    exponent = np.where(amax > 0, np.floor(np.log2(np.where(amax > 0, amax, 1.0))) - 2, 0).astype(np.int32)
+    exponent = np.clip(exponent, -127, 127)
+    scaled = blocks * np.exp2(-exponent.astype(np.float32))[:, :, None]
+    return pack_nibbles(e2m1_encode(scaled.reshape(rows, cols))), (exponent + 127).astype(np.uint8)
+
+
+def mxfp4_values(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """float64 values of an MXFP4 matrix."""
+    values = e2m1_decode(unpack_nibbles(packed)).astype(np.float64)
+    return values * np.repeat(np.exp2(scales.astype(np.float64) - 127), 32, axis=1)
+
+
+def gemm_mxfp4(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.ndarray, *, c_type: int = BF16, threads: int = 1) -> np.ndarray:
+    """C = sum over 32-wide K blocks of 2^(sa-127) 2^(sb-127) (a4 . b4): a (M, K/2), b (N, K/2) packed e2m1 codes, sa (M, K/32),
+    sb (N, K/32) e8m0 bytes."""
+    a, b = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(b, np.uint8)
+    sa, sb = np.ascontiguousarray(sa, np.uint8), np.ascontiguousarray(sb, np.uint8)
+    (m, k_bytes), n = a.shape, b.shape[0]
+    c = np.zeros((m, n), _NUMPY[c_type])
+    _run(_split(m, threads), lambda lo, hi: lib().krn_oracle_gemm_mxfp4(
+        c_type, _p(a), _p(sa), _p(b), _p(sb), _p(c), m, n, 2 * k_bytes, k_bytes, k_bytes, n, sa.shape[1], sb.shape[1], lo, hi))
+    return c
 
 
 def gemm_nvfp4(a: np.ndarray, sa: np.ndarray, b: np.ndarray, sb: np.ndarray, alpha: float = 1.0, *, c_type: int = BF16,

@@ -80,3 +80,18 @@ def test_nvfp4_quantiser_matches_the_oracle_and_the_format_tables() -> None:
                                   np.array([0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0, -6.0], np.float32))
     with pytest.raises(ValueError, match="whole 1 x 16 blocks"):
         ops.quantize_nvfp4_host(np.zeros((4, 24), np.float32))
+
+
+def test_mxfp4_quantiser_matches_the_oracle() -> None:
+    x = np.random.default_rng(15).standard_normal((24, 256)).astype(np.float32) * 5
+    packed, scales = ops.quantize_mxfp4_host(x)
+    want_packed, want_scales = o.quantize_mxfp4(x)
+    np.testing.assert_array_equal(packed, want_packed)
+    np.testing.assert_array_equal(scales, want_scales)
+    table = np.array(krn.formats.E2M1.table)
+    values = table[o.unpack_nibbles(packed)] * np.repeat(np.exp2(scales.astype(np.float64) - 127), 32, axis=1)
+    np.testing.assert_array_equal(values, o.mxfp4_values(packed, scales))
+    assert np.abs(values).max() <= np.abs(x).max() * 1.51  # the floor rule may leave the block maximum up to 1.5x above 6 * scale: it saturates
+    assert np.linalg.norm(values - x) / np.linalg.norm(x) < 0.16
+    with pytest.raises(ValueError, match="whole 1 x 32 blocks"):
+        ops.quantize_mxfp4_host(np.zeros((4, 48), np.float32))
