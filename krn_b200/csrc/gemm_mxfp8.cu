@@ -469,20 +469,19 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const bool live = row < (is_a ? p.m : p.n);
             const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) +
                                  (long long)kb0 * (4 * kWordsPerBlock);
-#pragma unroll
-            for (int k = 0; k < kWords; ++k) w[i][k] = kUnit;
-            if (live) {
+            if (live && words_here == kWords) {
+              // the common case, kept lean: this warp's instruction count is what the slot's turn-around is made of
 #pragma unroll
               for (int v = 0; v < kWords / 4; ++v) {
-                if (4 * v + 4 <= words_here) {
-                  const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
-                  w[i][4 * v] = x.x, w[i][4 * v + 1] = x.y, w[i][4 * v + 2] = x.z, w[i][4 * v + 3] = x.w;
-                } else {
-                  // the row ends inside this vector (MXFP8 with a K-block count that is not a multiple of four)
+                const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
+                w[i][4 * v] = x.x, w[i][4 * v + 1] = x.y, w[i][4 * v + 2] = x.z, w[i][4 * v + 3] = x.w;
+              }
+            } else {
+              // a row beyond the matrix (the code of 1.0 everywhere) or the last, shorter slot of a row
 #pragma unroll
-                  for (int k = 4 * v; k < 4 * v + 4; ++k)
-                    if (k < words_here) w[i][k] = __ldg(reinterpret_cast<const uint32_t*>(src) + k);
-                }
+              for (int k = 0; k < kWords; ++k) {
+                w[i][k] = kUnit;
+                if (live && k < words_here) w[i][k] = __ldg(reinterpret_cast<const uint32_t*>(src) + k);
               }
             }
           }
