@@ -70,7 +70,11 @@ struct Layout {
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
   // four instructions take four bytes each.
   static constexpr int kScaleSets = kWordsPerBlock;
-  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes;
+  // A pair's 4-bit kernel brings the scale rows of a ring slot in by TMA (below) and transposes them from shared memory:
+  // 32 bytes of padding after a K block's scale groups move consecutive K blocks eight banks apart, which makes the
+  // warp's transposing stores conflict-free.
+  static constexpr bool kStaged = FP4 && CTA_GROUP == 2;
+  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes + (kStaged ? 32 : 0);
   // K blocks of scales per ring slot. An MXFP8 pair takes eight (32 scale bytes per row): the peer's loaders signal the
   // leader with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide
   // that together with the global-memory latency behind the K blocks of the other slot; four were measured 17 %
@@ -78,11 +82,16 @@ struct Layout {
   // make room), two alone.
   static constexpr int kScaleChunk = (CTA_GROUP == 2 ? 8 : 4) / (FORMAT == kNvfp4 ? 2 : 1);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-  static constexpr int kStages = FP4 ? 4 : (CTA_GROUP == 2 ? 3 : 2);
+  static constexpr int kStages = FP4 ? (CTA_GROUP == 2 ? 3 : 4) : (CTA_GROUP == 2 ? 3 : 2);
   // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
   // cluster-scope arrive) does not fit behind one slot of four K blocks.
   static constexpr int kScaleSlots = (FP4 && CTA_GROUP == 2) ? 3 : 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kEpilogueBytes + 256 + 1024;
+  // the epilogue's staging buffers follow and are swizzled 128-byte rows: they start on a 1024-byte boundary
+  static constexpr int kScaleRingBytes = (kScaleSlots * kScaleSlotBytes + 1023) / 1024 * 1024;
+  // Staged scale rows: per loader warp one buffer of 384 rows (this CTA's 128 A rows, the tile's 256 B rows) x 64 bytes,
+  // the scale bytes of one ring slot exactly as they lie in global memory, written by three TMA boxes.
+  static constexpr int kStagingBytes = kStaged ? 384 * 64 : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + 2 * kStagingBytes + kEpilogueBytes + 256 + 1024;
 };
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
@@ -96,11 +105,12 @@ struct MxScales {
   const uint8_t* sb;  // [N, K / 32] e8m0, or [N, K / 16] e4m3
   long long ldsa, ldsb;  // row pitches in bytes
   int vector_ok;         // both addresses and pitches are multiples of 16: 16 scale bytes of a row come in one load
+  int staged;            // 4-bit pair kernel: the scale rows come in through the two scale tensor maps
   float alpha;           // NVFP4: product of the two tensor scales, applied to the finished accumulator
 };
 
 enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
-            kSiteScaleEmpty = 46 };
+            kSiteScaleEmpty = 46, kSiteScaleStaged = 47 };
 
 
 // Instruction descriptor of kind::mxf8f6f4.block_scale: B scale id [4,6), A format [7,10), B format [10,13), majors 15 /
@@ -196,7 +206,8 @@ __device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t sm
 template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ CUtensorMap map_c, Problem p, MxScales scales, DeviceStatus* status) {
+                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_sa,
+                  const __grid_constant__ CUtensorMap map_sb, Problem p, MxScales scales, DeviceStatus* status) {
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
   using L = Layout<CTA_GROUP, FORMAT>;
@@ -218,15 +229,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   const uint32_t stages_addr = base;
   const uint32_t scale_addr = base + kStages * kStageBytes;
-  const uint32_t epilogue_addr = scale_addr + kScaleSlots * kScaleSlotBytes;
-  uint8_t* tail = smem + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kEpilogueBytes;
+  const uint32_t staging_addr = scale_addr + L::kScaleRingBytes;
+  const uint32_t epilogue_addr = staging_addr + 2 * L::kStagingBytes;
+  uint8_t* tail = smem + kStages * kStageBytes + L::kScaleRingBytes + 2 * L::kStagingBytes + kEpilogueBytes;
   const uint32_t full_bar = smem_u32(tail);                  // [kStages]
   const uint32_t empty_bar = full_bar + 8 * kStages;         // [kStages]
   const uint32_t scale_full_bar = empty_bar + 8 * kStages;            // [kScaleSlots]
   const uint32_t scale_empty_bar = scale_full_bar + 8 * kScaleSlots;  // [kScaleSlots]
   const uint32_t tmem_full_bar = scale_empty_bar + 8 * kScaleSlots;
   const uint32_t tmem_empty_bar = tmem_full_bar + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 2));
+  const uint32_t staging_full_bar = tmem_empty_bar + 8;      // [2]: one per loader warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -249,11 +262,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     mbar_init(tmem_full_bar, 1);
     mbar_init(tmem_empty_bar, 4 * CTA_GROUP);            // the epilogue warps of every CTA of the tile
+    mbar_init(staging_full_bar, 1);
+    mbar_init(staging_full_bar + 8, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
     prefetch_tensormap(&map_c);
+    if (L::kStaged && scales.staged) {
+      prefetch_tensormap(&map_sa);
+      prefetch_tensormap(&map_sb);
+    }
   }
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
@@ -431,7 +450,89 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // get the code of 1.0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
     const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
-    if (FP4 || scales.vector_ok) {
+    if (L::kStaged && scales.staged) {
+      // 4-bit pair: a slot's scale bytes are 64 per row, 24 KB per CTA, and fetching them with the warp's own loads made
+      // the loaders the slowest part of the kernel (a loader warp's turn took two slot periods, most of it issuing 48
+      // loads). Here a loader warp's elected lane has TMA write the 384 rows of its next slot into the warp's staging
+      // buffer as they lie in global memory (three boxes of 128 rows x 64 bytes; rows beyond the matrix and bytes past
+      // a row's end arrive as zeros, and so do the codes they scale), and the warp only transposes shared memory ->
+      // shared memory into the layout tcgen05.cp wants. The two warps take alternate slots; a warp asks for its next
+      // slot's rows as soon as it has read the staging buffer out.
+      // Lane mapping of a pass: lane = j * 8 + e * 4 + piece takes the 16 bytes `piece` of row 2 * pass + e + 32 * j of
+      // a 128-row group: eight lanes read 128 contiguous bytes, and the 32 lanes' stores of one word fall on 32 banks
+      // (rows r, r + 32, r + 64, r + 96 are the four words of one 16-byte line of the layout).
+      const int mine = warp - 2;
+      const uint32_t staging = staging_addr + mine * L::kStagingBytes;
+      const uint8_t* staging_ptr = smem + (staging - base);
+      const uint32_t staging_bar = staging_full_bar + 8 * mine;
+      struct Cursor { int t, kb0, index; };
+      auto step = [&](Cursor& c) {
+        c.kb0 += kScaleChunk;
+        ++c.index;
+        if (c.kb0 >= num_kb) c.kb0 = 0, c.t += tile_step;
+      };
+      auto to_mine = [&](Cursor& c) {
+        while (c.t < num_tiles && (c.index & 1) != mine) step(c);
+      };
+      auto fetch = [&](const Cursor& c) {  // one lane
+        int tm, tn;
+        tile_coords(c.t, p, tm, tn);
+        const int x = c.kb0 * (4 * kWordsPerBlock);  // a multiple of 64 bytes
+        mbar_arrive_expect_tx(staging_bar, 384u * 64u);
+        tma_load_2d(staging, &map_sa, x, tm * (kBM * CTA_GROUP) + int(rank) * kBM, staging_bar);
+        tma_load_2d(staging + 128 * 64, &map_sb, x, tn * kBN, staging_bar);
+        tma_load_2d(staging + 256 * 64, &map_sb, x, tn * kBN + 128, staging_bar);
+      };
+      Cursor cur = {first_tile, 0, 0};
+      to_mine(cur);
+      if (lane == 0 && cur.t < num_tiles) fetch(cur);
+      uint32_t staging_phase = 0;
+      const int piece = int(lane) & 3, row_in_pass = (int(lane) >> 2 & 1) + 32 * (int(lane) >> 3);
+      uint32_t place[4];  // where the lane's four words of a row go, relative to the row's word of K block 0, set 0
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int word = 4 * piece + k;
+        place[k] = (word / kWordsPerBlock) * kScaleBlockBytes + (word % kWordsPerBlock) * kScaleGroupBytes;
+      }
+      while (cur.t < num_tiles) {
+        const uint32_t slot = uint32_t(cur.index) % kScaleSlots, slot_phase = (uint32_t(cur.index) / kScaleSlots) & 1u;
+        if (!__all_sync(0xffffffffu, mbar_wait(staging_bar, staging_phase, abort_flag, status, kSiteScaleStaged))) break;
+        staging_phase ^= 1u;
+        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
+                                               kSiteScaleEmpty))) {
+          break;
+        }
+        uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
+#pragma unroll
+        for (int batch = 0; batch < 6; ++batch) {  // 48 passes, eight loads in flight
+          uint4 x[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int pass = batch * 8 + i, group = pass >> 4, in_group = 2 * (pass & 15) + row_in_pass;
+            x[i] = *reinterpret_cast<const uint4*>(staging_ptr + (group * 128 + in_group) * 64 + piece * 16);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int pass = batch * 8 + i, group = pass >> 4, in_group = 2 * (pass & 15) + row_in_pass;
+            uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
+            *reinterpret_cast<uint32_t*>(dst + place[0]) = x[i].x;
+            *reinterpret_cast<uint32_t*>(dst + place[1]) = x[i].y;
+            *reinterpret_cast<uint32_t*>(dst + place[2]) = x[i].z;
+            *reinterpret_cast<uint32_t*>(dst + place[3]) = x[i].w;
+          }
+        }
+        Cursor next = cur;
+        step(next);
+        to_mine(next);
+        fence_async_smem();  // the slot's words for tcgen05.cp, and this warp's reads of the staging buffer before TMA refills it
+        __syncwarp();
+        if (lane == 0) {
+          if (next.t < num_tiles) fetch(next);
+          mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
+        }
+        cur = next;
+      }
+    } else if (FP4 || scales.vector_ok) {
       // Filling a ring slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive
       // (about 1000) — and a trace of the issuing warp showed it waiting for scale factors 2000-2900 cycles of every
       // slot when both loader warps worked on every slot one after the other. So the two loader warps take ALTERNATE
@@ -702,8 +803,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
-int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, Problem p,
-           MxScales scales, cudaStream_t stream) {
+int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+           const CUtensorMap& msa, const CUtensorMap& msb, Problem p, MxScales scales, cudaStream_t stream) {
   using L = Layout<CTA_GROUP, FORMAT>;
   auto kernel = gemm_mxfp8_kernel<CTA_GROUP, FORMAT, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
@@ -722,16 +823,16 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, p, scales, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, msa, msb, p, scales, ctx->status_dev));
   return KRN_B200_OK;
 }
 
 template <int CTA_GROUP, int FORMAT>
 int launch_for_output(const DeviceContext* ctx, int c_type, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                      Problem p, MxScales scales, cudaStream_t stream) {
-  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FORMAT, float, false>(ctx, ma, mb, mc, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FORMAT, uint16_t, true>(ctx, ma, mb, mc, p, scales, stream);
-  return launch<CTA_GROUP, FORMAT, uint16_t, false>(ctx, ma, mb, mc, p, scales, stream);
+                      const CUtensorMap& msa, const CUtensorMap& msb, Problem p, MxScales scales, cudaStream_t stream) {
+  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FORMAT, float, false>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FORMAT, uint16_t, true>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
+  return launch<CTA_GROUP, FORMAT, uint16_t, false>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
 }
 
 // Checks shared by the two entry points, the tensor maps (operand rows as bytes: 128 per K block) and the launch.
@@ -770,7 +871,9 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
   p.b_kn = 0;
-  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, alpha};
+  // scale rows of at least one ring slot (64 bytes) come in by TMA in the 4-bit pair kernel
+  const bool staged = FP4 && group == 2 && scale_bytes >= 64;
+  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, staged ? 1 : 0, alpha};
 
   CUtensorMap map_a, map_b, map_c;
   {
@@ -794,8 +897,16 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  if (group == 2) return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
-  return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, p, scales, stream);
+  CUtensorMap map_sa = {}, map_sb = {};
+  if (staged) {
+    uint32_t box[2] = {64, 128};
+    uint64_t dims_a[2] = {uint64_t(scale_bytes), uint64_t(m)}, dims_b[2] = {uint64_t(scale_bytes), uint64_t(n)};
+    uint64_t stride_a[1] = {uint64_t(ldsa)}, stride_b[1] = {uint64_t(ldsb)};
+    if (int rc = encode_tensor_map(&map_sa, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sa, dims_a, stride_a, box, Swizzle::kNone)) return rc;
+    if (int rc = encode_tensor_map(&map_sb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sb, dims_b, stride_b, box, Swizzle::kNone)) return rc;
+  }
+  if (group == 2) return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_sa, map_sb, p, scales, stream);
+  return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_sa, map_sb, p, scales, stream);
 }
 
 }  // namespace
