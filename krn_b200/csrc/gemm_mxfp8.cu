@@ -66,15 +66,15 @@ struct Layout {
   // flight (with two 64 KB stages only one is ever being filled, and the TMA round trip then sets the K-block rate): its
   // stages are single K blocks, five of them in a pair.
   static constexpr int kBlocksPerStage = FP4 ? 1 : 2;
-  static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes;
+  // A pair's 4-bit kernel reads its scale bytes from a copy that a small kernel has laid out beforehand the way
+  // tcgen05.cp wants them: they then arrive by TMA with the operands, as part of the stage (one 512-byte atom per set).
+  static constexpr bool kPretiled = FP4 && CTA_GROUP == 2;
+  static constexpr int kStageScaleBytes = kPretiled ? 3 * kWordsPerBlock * 512 : 0;  // A rows, B rows 0-127, B rows 128-255
+  static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes + kStageScaleBytes;
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
   // four instructions take four bytes each.
   static constexpr int kScaleSets = kWordsPerBlock;
-  // A pair's 4-bit kernel brings the scale rows of a ring slot in by TMA (below) and transposes them from shared memory:
-  // 32 bytes of padding after a K block's scale groups move consecutive K blocks eight banks apart, which makes the
-  // warp's transposing stores conflict-free.
-  static constexpr bool kStaged = FP4 && CTA_GROUP == 2;
-  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes + (kStaged ? 32 : 0);
+  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes;
   // K blocks of scales per ring slot. An MXFP8 pair takes eight (32 scale bytes per row): the peer's loaders signal the
   // leader with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide
   // that together with the global-memory latency behind the K blocks of the other slot; four were measured 17 %
@@ -82,16 +82,13 @@ struct Layout {
   // make room), two alone.
   static constexpr int kScaleChunk = (CTA_GROUP == 2 ? 8 : 4) / (FORMAT == kNvfp4 ? 2 : 1);
   static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-  static constexpr int kStages = FP4 ? (CTA_GROUP == 2 ? 3 : 4) : (CTA_GROUP == 2 ? 3 : 2);
+  static constexpr int kStages = FP4 ? (kPretiled ? 5 : 4) : (CTA_GROUP == 2 ? 3 : 2);
   // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
   // cluster-scope arrive) does not fit behind one slot of four K blocks.
   static constexpr int kScaleSlots = (FP4 && CTA_GROUP == 2) ? 3 : 2;
   // the epilogue's staging buffers follow and are swizzled 128-byte rows: they start on a 1024-byte boundary
-  static constexpr int kScaleRingBytes = (kScaleSlots * kScaleSlotBytes + 1023) / 1024 * 1024;
-  // Staged scale rows: per loader warp one buffer of 384 rows (this CTA's 128 A rows, the tile's 256 B rows) x 64 bytes,
-  // the scale bytes of one ring slot exactly as they lie in global memory, written by three TMA boxes.
-  static constexpr int kStagingBytes = kStaged ? 384 * 64 : 0;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + 2 * kStagingBytes + kEpilogueBytes + 256 + 1024;
+  static constexpr int kScaleRingBytes = kPretiled ? 0 : (kScaleSlots * kScaleSlotBytes + 1023) / 1024 * 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kEpilogueBytes + 256 + 1024;
 };
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
@@ -105,12 +102,12 @@ struct MxScales {
   const uint8_t* sb;  // [N, K / 32] e8m0, or [N, K / 16] e4m3
   long long ldsa, ldsb;  // row pitches in bytes
   int vector_ok;         // both addresses and pitches are multiples of 16: 16 scale bytes of a row come in one load
-  int staged;            // 4-bit pair kernel: the scale rows come in through the two scale tensor maps
+  int b_atom0;           // 4-bit pair kernel: first 512-byte atom of B's scales in the pre-tiled copy (A's start at 0)
   float alpha;           // NVFP4: product of the two tensor scales, applied to the finished accumulator
 };
 
 enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
-            kSiteScaleEmpty = 46, kSiteScaleStaged = 47 };
+            kSiteScaleEmpty = 46 };
 
 
 // Instruction descriptor of kind::mxf8f6f4.block_scale: B scale id [4,6), A format [7,10), B format [10,13), majors 15 /
@@ -206,8 +203,8 @@ __device__ __forceinline__ void scales_to_tmem(uint32_t tmem_column, uint32_t sm
 template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_sa,
-                  const __grid_constant__ CUtensorMap map_sb, Problem p, MxScales scales, DeviceStatus* status) {
+                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_scales,
+                  Problem p, MxScales scales, DeviceStatus* status) {
   constexpr int kChunkCols = 128 / int(sizeof(OutT));  // output columns per 128-byte store row
   constexpr int kChunks = kBN / kChunkCols;
   using L = Layout<CTA_GROUP, FORMAT>;
@@ -229,17 +226,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   const uint32_t stages_addr = base;
   const uint32_t scale_addr = base + kStages * kStageBytes;
-  const uint32_t staging_addr = scale_addr + L::kScaleRingBytes;
-  const uint32_t epilogue_addr = staging_addr + 2 * L::kStagingBytes;
-  uint8_t* tail = smem + kStages * kStageBytes + L::kScaleRingBytes + 2 * L::kStagingBytes + kEpilogueBytes;
+  const uint32_t epilogue_addr = scale_addr + L::kScaleRingBytes;
+  uint8_t* tail = smem + kStages * kStageBytes + L::kScaleRingBytes + kEpilogueBytes;
   const uint32_t full_bar = smem_u32(tail);                  // [kStages]
   const uint32_t empty_bar = full_bar + 8 * kStages;         // [kStages]
   const uint32_t scale_full_bar = empty_bar + 8 * kStages;            // [kScaleSlots]
   const uint32_t scale_empty_bar = scale_full_bar + 8 * kScaleSlots;  // [kScaleSlots]
   const uint32_t tmem_full_bar = scale_empty_bar + 8 * kScaleSlots;
   const uint32_t tmem_empty_bar = tmem_full_bar + 8;
-  const uint32_t staging_full_bar = tmem_empty_bar + 8;      // [2]: one per loader warp
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 4));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -262,17 +257,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     mbar_init(tmem_full_bar, 1);
     mbar_init(tmem_empty_bar, 4 * CTA_GROUP);            // the epilogue warps of every CTA of the tile
-    mbar_init(staging_full_bar, 1);
-    mbar_init(staging_full_bar + 8, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
     prefetch_tensormap(&map_c);
-    if (L::kStaged && scales.staged) {
-      prefetch_tensormap(&map_sa);
-      prefetch_tensormap(&map_sb);
-    }
+    if (L::kPretiled) prefetch_tensormap(&map_scales);
   }
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
@@ -313,11 +303,24 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           } else {
             // both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both
-            if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * 2u * kBlockBytes);
+            if (rank == 0) {
+              mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * 2u * kBlockBytes + 2u * L::kStageScaleBytes);
+            }
             const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
             for (int j = 0; j < blocks; ++j) {
               tma_load_2d_pair(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, leader_full);
               tma_load_2d_pair(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, leader_full);
+            }
+            if constexpr (L::kPretiled) {
+              // this K block's scale atoms, already in tcgen05.cp's layout: this CTA's group of 128 A rows and both
+              // groups of the tile's B rows (rows of the copy = atoms of 512 bytes, one per 128-row group, K block and set)
+              constexpr int kSets = L::kScaleSets;
+              const uint32_t sdst = dst + kBlockBytes;
+              const int a_atom = ((tm * CTA_GROUP + int(rank)) * num_kb + kb) * kSets;
+              const int b_atom = scales.b_atom0 + (tn * 2 * num_kb + kb) * kSets;
+              tma_load_2d_pair(sdst, &map_scales, 0, a_atom, leader_full);
+              tma_load_2d_pair(sdst + kSets * 512, &map_scales, 0, b_atom, leader_full);
+              tma_load_2d_pair(sdst + 2 * kSets * 512, &map_scales, 0, b_atom + num_kb * kSets, leader_full);
             }
           }
           if (++stage == kStages) {
@@ -360,22 +363,31 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           for (int j = 0; j < blocks && ok; ++j) {
             const int kb = kb0 + j;
             const int in_chunk = kb & (kScaleChunk - 1);
-            if (in_chunk == 0) {
-              if (!wait(scale_full_bar + 8 * slot, slot_phase, kSiteMmaScale)) {
-                ok = false;
-                break;
+            if constexpr (!L::kPretiled) {
+              if (in_chunk == 0) {
+                if (!wait(scale_full_bar + 8 * slot, slot_phase, kSiteMmaScale)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
               }
-              tc_fence_after();
             }
+            const bool slot_done = !L::kPretiled && (in_chunk == kScaleChunk - 1 || kb == num_kb - 1);
+            // where this K block's scale groups lie: in the ring slot (sets 1536 bytes apart, each A | B | B), or, for
+            // the pre-tiled copy, behind the stage's operands (A's sets, then the sets of each group of B rows)
+            const uint32_t in_stage = stages_addr + stage * kStageBytes + kBlockBytes;
             const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
-            const bool slot_done = in_chunk == kScaleChunk - 1 || kb == num_kb - 1;
+            const uint32_t group_a = L::kPretiled ? in_stage : block;
+            const uint32_t group_b0 = L::kPretiled ? in_stage + L::kScaleSets * 512 : block + 512;
+            const uint32_t group_b1 = L::kPretiled ? in_stage + 2 * L::kScaleSets * 512 : block + 1024;
+            constexpr uint32_t kSetStride = L::kPretiled ? 512 : kScaleGroupBytes;
             if (leader) {
               const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
               const uint32_t b_lo = a_lo + (kABytes >> 4);
               if constexpr (!FP4) {
-                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, block);
-                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, block + 512);
-                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, block + 1024);
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleA, group_a);
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB, group_b0);
+                scales_to_tmem<CTA_GROUP>(tmem_base + kTmemScaleB + 4, group_b1);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                   umma_mx<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mx_idesc(ks, kBM * CTA_GROUP),
@@ -385,11 +397,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                   // each 64-code instruction has its own scale bytes, in its own tensor-memory columns
-                  const uint32_t set = block + ks * kScaleGroupBytes;
                   const uint32_t sfa = tmem_base + kTmemScaleA + 12 * ks, sfb = tmem_base + kTmemScaleB + 12 * ks;
-                  scales_to_tmem<CTA_GROUP>(sfa, set);
-                  scales_to_tmem<CTA_GROUP>(sfb, set + 512);
-                  scales_to_tmem<CTA_GROUP>(sfb + 4, set + 1024);
+                  scales_to_tmem<CTA_GROUP>(sfa, group_a + ks * kSetStride);
+                  scales_to_tmem<CTA_GROUP>(sfb, group_b0 + ks * kSetStride);
+                  scales_to_tmem<CTA_GROUP>(sfb + 4, group_b1 + ks * kSetStride);
                   umma_nvf4<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, nvf4_idesc(kBM * CTA_GROUP), sfa, sfb,
                                        (kb > 0 || ks > 0) ? 1u : 0u);
                 }
@@ -399,10 +410,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   // MXFP4: two 64-code instructions share a set of scale columns; each takes two of the four bytes
                   const uint32_t sfa = tmem_base + kTmemScaleA + 12 * (ks >> 1), sfb = tmem_base + kTmemScaleB + 12 * (ks >> 1);
                   if ((ks & 1) == 0) {
-                    const uint32_t set = block + (ks >> 1) * kScaleGroupBytes;
-                    scales_to_tmem<CTA_GROUP>(sfa, set);
-                    scales_to_tmem<CTA_GROUP>(sfb, set + 512);
-                    scales_to_tmem<CTA_GROUP>(sfb + 4, set + 1024);
+                    scales_to_tmem<CTA_GROUP>(sfa, group_a + (ks >> 1) * kSetStride);
+                    scales_to_tmem<CTA_GROUP>(sfb, group_b0 + (ks >> 1) * kSetStride);
+                    scales_to_tmem<CTA_GROUP>(sfb + 4, group_b1 + (ks >> 1) * kSetStride);
                   }
                   umma_mxf4<CTA_GROUP>(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, desc_hi, mxf4_idesc((ks & 1) * 2, kBM * CTA_GROUP), sfa,
                                        sfb, (kb > 0 || ks > 0) ? 1u : 0u);
@@ -450,88 +460,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // get the code of 1.0 (their codes are zero-filled by TMA, the product stays zero).
     const int tid = int(threadIdx.x) - 64;
     const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
-    if (L::kStaged && scales.staged) {
-      // 4-bit pair: a slot's scale bytes are 64 per row, 24 KB per CTA, and fetching them with the warp's own loads made
-      // the loaders the slowest part of the kernel (a loader warp's turn took two slot periods, most of it issuing 48
-      // loads). Here a loader warp's elected lane has TMA write the 384 rows of its next slot into the warp's staging
-      // buffer as they lie in global memory (three boxes of 128 rows x 64 bytes; rows beyond the matrix and bytes past
-      // a row's end arrive as zeros, and so do the codes they scale), and the warp only transposes shared memory ->
-      // shared memory into the layout tcgen05.cp wants. The two warps take alternate slots; a warp asks for its next
-      // slot's rows as soon as it has read the staging buffer out.
-      // Lane mapping of a pass: lane = j * 8 + e * 4 + piece takes the 16 bytes `piece` of row 2 * pass + e + 32 * j of
-      // a 128-row group: eight lanes read 128 contiguous bytes, and the 32 lanes' stores of one word fall on 32 banks
-      // (rows r, r + 32, r + 64, r + 96 are the four words of one 16-byte line of the layout).
-      const int mine = warp - 2;
-      const uint32_t staging = staging_addr + mine * L::kStagingBytes;
-      const uint8_t* staging_ptr = smem + (staging - base);
-      const uint32_t staging_bar = staging_full_bar + 8 * mine;
-      struct Cursor { int t, kb0, index; };
-      auto step = [&](Cursor& c) {
-        c.kb0 += kScaleChunk;
-        ++c.index;
-        if (c.kb0 >= num_kb) c.kb0 = 0, c.t += tile_step;
-      };
-      auto to_mine = [&](Cursor& c) {
-        while (c.t < num_tiles && (c.index & 1) != mine) step(c);
-      };
-      auto fetch = [&](const Cursor& c) {  // one lane
-        int tm, tn;
-        tile_coords(c.t, p, tm, tn);
-        const int x = c.kb0 * (4 * kWordsPerBlock);  // a multiple of 64 bytes
-        mbar_arrive_expect_tx(staging_bar, 384u * 64u);
-        tma_load_2d(staging, &map_sa, x, tm * (kBM * CTA_GROUP) + int(rank) * kBM, staging_bar);
-        tma_load_2d(staging + 128 * 64, &map_sb, x, tn * kBN, staging_bar);
-        tma_load_2d(staging + 256 * 64, &map_sb, x, tn * kBN + 128, staging_bar);
-      };
-      Cursor cur = {first_tile, 0, 0};
-      to_mine(cur);
-      if (lane == 0 && cur.t < num_tiles) fetch(cur);
-      uint32_t staging_phase = 0;
-      const int piece = int(lane) & 3, row_in_pass = (int(lane) >> 2 & 1) + 32 * (int(lane) >> 3);
-      uint32_t place[4];  // where the lane's four words of a row go, relative to the row's word of K block 0, set 0
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int word = 4 * piece + k;
-        place[k] = (word / kWordsPerBlock) * kScaleBlockBytes + (word % kWordsPerBlock) * kScaleGroupBytes;
-      }
-      while (cur.t < num_tiles) {
-        const uint32_t slot = uint32_t(cur.index) % kScaleSlots, slot_phase = (uint32_t(cur.index) / kScaleSlots) & 1u;
-        if (!__all_sync(0xffffffffu, mbar_wait(staging_bar, staging_phase, abort_flag, status, kSiteScaleStaged))) break;
-        staging_phase ^= 1u;
-        if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
-                                               kSiteScaleEmpty))) {
-          break;
-        }
-        uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-#pragma unroll
-        for (int batch = 0; batch < 6; ++batch) {  // 48 passes, eight loads in flight
-          uint4 x[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int pass = batch * 8 + i, group = pass >> 4, in_group = 2 * (pass & 15) + row_in_pass;
-            x[i] = *reinterpret_cast<const uint4*>(staging_ptr + (group * 128 + in_group) * 64 + piece * 16);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int pass = batch * 8 + i, group = pass >> 4, in_group = 2 * (pass & 15) + row_in_pass;
-            uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
-            *reinterpret_cast<uint32_t*>(dst + place[0]) = x[i].x;
-            *reinterpret_cast<uint32_t*>(dst + place[1]) = x[i].y;
-            *reinterpret_cast<uint32_t*>(dst + place[2]) = x[i].z;
-            *reinterpret_cast<uint32_t*>(dst + place[3]) = x[i].w;
-          }
-        }
-        Cursor next = cur;
-        step(next);
-        to_mine(next);
-        fence_async_smem();  // the slot's words for tcgen05.cp, and this warp's reads of the staging buffer before TMA refills it
-        __syncwarp();
-        if (lane == 0) {
-          if (next.t < num_tiles) fetch(next);
-          mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
-        }
-        cur = next;
-      }
+    if constexpr (L::kPretiled) {
+      // nothing to load: the scale atoms of a K block arrive with its operands (the producer warp's TMA)
     } else if (FP4 || scales.vector_ok) {
       // Filling a ring slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive
       // (about 1000) — and a trace of the issuing warp showed it waiting for scale factors 2000-2900 cycles of every
@@ -802,9 +732,34 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// Scale bytes of one operand, row-major [rows, num_kb * 4 * SETS], into tcgen05.cp's layout: per group of 128 rows, K
+// block and set one atom of 128 words, word (row % 32) * 4 + row / 32 = the set's four scale bytes of that row. Thread t
+// of a block takes row (t % 4) * 32 + t / 4 of the group, whose word is word t: the stores of a warp are contiguous.
+// Rows beyond the matrix become zeros (their codes are zero-filled by TMA).
+template <int SETS>
+__global__ void __launch_bounds__(128)
+tile_scales_kernel(const uint8_t* __restrict__ src, long long ld, long long rows, int num_kb, uint32_t* __restrict__ out) {
+  const int group = blockIdx.x, kb = blockIdx.y, t = threadIdx.x;
+  const long long row = (long long)group * 128 + (t & 3) * 32 + (t >> 2);
+  uint32_t words[SETS] = {};
+  if (row < rows) {
+    const uint8_t* from = src + row * ld + (long long)kb * (4 * SETS);
+    if constexpr (SETS == 4) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(from));
+      words[0] = v.x, words[1] = v.y, words[2] = v.z, words[3] = v.w;
+    } else {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(from));
+      words[0] = v.x, words[1] = v.y;
+    }
+  }
+  uint32_t* to = out + ((long long)group * num_kb + kb) * (SETS * 128) + t;
+#pragma unroll
+  for (int set = 0; set < SETS; ++set) to[set * 128] = words[set];
+}
+
 template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
 int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-           const CUtensorMap& msa, const CUtensorMap& msb, Problem p, MxScales scales, cudaStream_t stream) {
+           const CUtensorMap& ms, Problem p, MxScales scales, cudaStream_t stream) {
   using L = Layout<CTA_GROUP, FORMAT>;
   auto kernel = gemm_mxfp8_kernel<CTA_GROUP, FORMAT, OutT, OUT_BF16>;
   KRNB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes));
@@ -823,16 +778,16 @@ int launch(const DeviceContext* ctx, const CUtensorMap& ma, const CUtensorMap& m
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, msa, msb, p, scales, ctx->status_dev));
+  KRNB_CUDA(cudaLaunchKernelEx(&config, kernel, ma, mb, mc, ms, p, scales, ctx->status_dev));
   return KRN_B200_OK;
 }
 
 template <int CTA_GROUP, int FORMAT>
 int launch_for_output(const DeviceContext* ctx, int c_type, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                      const CUtensorMap& msa, const CUtensorMap& msb, Problem p, MxScales scales, cudaStream_t stream) {
-  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FORMAT, float, false>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
-  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FORMAT, uint16_t, true>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
-  return launch<CTA_GROUP, FORMAT, uint16_t, false>(ctx, ma, mb, mc, msa, msb, p, scales, stream);
+                      const CUtensorMap& ms, Problem p, MxScales scales, cudaStream_t stream) {
+  if (c_type == KRN_B200_F32) return launch<CTA_GROUP, FORMAT, float, false>(ctx, ma, mb, mc, ms, p, scales, stream);
+  if (c_type == KRN_B200_BF16) return launch<CTA_GROUP, FORMAT, uint16_t, true>(ctx, ma, mb, mc, ms, p, scales, stream);
+  return launch<CTA_GROUP, FORMAT, uint16_t, false>(ctx, ma, mb, mc, ms, p, scales, stream);
 }
 
 // Checks shared by the two entry points, the tensor maps (operand rows as bytes: 128 per K block) and the launch.
@@ -871,9 +826,7 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
   p.b_kn = 0;
-  // scale rows of at least one ring slot (64 bytes) come in by TMA in the 4-bit pair kernel
-  const bool staged = FP4 && group == 2 && scale_bytes >= 64;
-  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, staged ? 1 : 0, alpha};
+  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, 0, alpha};
 
   CUtensorMap map_a, map_b, map_c;
   {
@@ -897,16 +850,45 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  CUtensorMap map_sa = {}, map_sb = {};
-  if (staged) {
-    uint32_t box[2] = {64, 128};
-    uint64_t dims_a[2] = {uint64_t(scale_bytes), uint64_t(m)}, dims_b[2] = {uint64_t(scale_bytes), uint64_t(n)};
-    uint64_t stride_a[1] = {uint64_t(ldsa)}, stride_b[1] = {uint64_t(ldsb)};
-    if (int rc = encode_tensor_map(&map_sa, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sa, dims_a, stride_a, box, Swizzle::kNone)) return rc;
-    if (int rc = encode_tensor_map(&map_sb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sb, dims_b, stride_b, box, Swizzle::kNone)) return rc;
+  CUtensorMap map_scales = {};
+  if (group == 1) return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
+  if constexpr (!FP4) {
+    return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
+  } else {
+    // The 4-bit pair kernel reads its scale bytes from a copy in tcgen05.cp's layout, made here by a small kernel on the
+    // same stream: 512-byte atoms, one per group of 128 rows, K block and set, A's groups first (two per tile row,
+    // padded with zeros), then B's. The copy lives in stream-ordered memory for the length of the call.
+    constexpr int kSets = Layout<2, FORMAT>::kScaleSets;
+    const int num_kb = int(k_bytes / kBK);
+    const long long groups_a = 2LL * p.tiles_m, groups_b = 2LL * p.tiles_n;
+    const long long atoms_a = groups_a * num_kb * kSets, atoms_b = groups_b * num_kb * kSets;
+    if (num_kb > 65535 || atoms_a + atoms_b > INT32_MAX) {
+      return fail(KRN_B200_ERR_UNSUPPORTED, "a 4-bit product of this size is not available: its scale copy would have %lld "
+                  "atoms. Instead: split the product along M or N", atoms_a + atoms_b);
+    }
+    uint32_t* tiled = nullptr;
+    KRNB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&tiled), size_t(atoms_a + atoms_b) * 512, ctx->scratch_pool,
+                                      stream));
+    tile_scales_kernel<kSets><<<dim3(unsigned(groups_a), unsigned(num_kb)), 128, 0, stream>>>(sa, ldsa, m, num_kb, tiled);
+    tile_scales_kernel<kSets><<<dim3(unsigned(groups_b), unsigned(num_kb)), 128, 0, stream>>>(sb, ldsb, n, num_kb,
+                                                                                          tiled + atoms_a * 128);
+    int rc = KRN_B200_OK;
+    if (cudaError_t err = cudaGetLastError(); err != cudaSuccess) {
+      rc = fail(KRN_B200_ERR_CUDA, "launch of the scale layout kernel failed: %s", cudaGetErrorString(err));
+    }
+    if (rc == KRN_B200_OK) {
+      uint64_t dims[2] = {128, uint64_t(atoms_a + atoms_b)};
+      uint64_t strides[1] = {512};
+      uint32_t box[2] = {128, uint32_t(kSets)};
+      rc = encode_tensor_map(&map_scales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, tiled, dims, strides, box, Swizzle::kNone);
+    }
+    if (rc == KRN_B200_OK) {
+      scales.b_atom0 = int(atoms_a);
+      rc = launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
+    }
+    cudaFreeAsync(tiled, stream);  // after the product in stream order
+    return rc;
   }
-  if (group == 2) return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_sa, map_sb, p, scales, stream);
-  return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_sa, map_sb, p, scales, stream);
 }
 
 }  // namespace

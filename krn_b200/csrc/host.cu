@@ -80,6 +80,20 @@ DeviceContext* current_context() {
     fail(KRN_B200_ERR_CUDA, "%s: %s (status word mapping)", cudaGetErrorName(err), cudaGetErrorString(err));
     return nullptr;
   }
+  cudaMemPoolProps pool_props = {};
+  pool_props.allocType = cudaMemAllocationTypePinned;
+  pool_props.handleTypes = cudaMemHandleTypeNone;
+  pool_props.location.type = cudaMemLocationTypeDevice;
+  pool_props.location.id = device;
+  err = cudaMemPoolCreate(&ctx.scratch_pool, &pool_props);
+  if (err == cudaSuccess) {
+    uint64_t keep = UINT64_MAX;  // never hand memory back at a synchronisation
+    err = cudaMemPoolSetAttribute(ctx.scratch_pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  if (err != cudaSuccess) {
+    fail(KRN_B200_ERR_CUDA, "%s: %s (scratch memory pool)", cudaGetErrorName(err), cudaGetErrorString(err));
+    return nullptr;
+  }
   g_contexts[device] = ctx;
   g_ready[device] = true;
   return &g_contexts[device];

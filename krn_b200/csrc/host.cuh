@@ -37,6 +37,9 @@ struct DeviceContext {
   int cc_minor = 0;
   DeviceStatus* status_host = nullptr;  // pinned, mapped
   DeviceStatus* status_dev = nullptr;   // device view of the same word
+  // Stream-ordered scratch memory that lives for one call (cudaMallocFromPoolAsync / cudaFreeAsync on the call's
+  // stream). The pool keeps what it has been given, so only the first call of a size reaches the driver's allocator.
+  cudaMemPool_t scratch_pool = nullptr;
 };
 
 // Context of the current device; created on first use (allocates the 16-byte status word once).
