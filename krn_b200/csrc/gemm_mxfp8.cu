@@ -10,19 +10,24 @@
 // own 128 x 256 half of the accumulator) whenever M > 128, else one CTA on a 128 x 256 tile. The pair moves 32 KB per K
 // block and CTA through L2 and shared memory instead of 48 KB, which is what the single-CTA form is limited by.
 //
-// Roles per CTA (256 threads, persistent over tiles):
-//   warp 0      TMA producer: A and B tiles of 128 codes per row into a ring of stages of TWO K blocks each (3 x 64 KB
-//               paired, 2 x 96 KB alone): one barrier per 256 codes of K halves the issuing thread's polls and commits
-//   warp 1      MMA issuer: per K block of 128 codes, copies that block's scale factors from shared memory into tensor
-//               memory (tcgen05.cp, 32x128b.warpx4: one 512-byte group per 128 rows) and issues four K = 32
-//               instructions whose descriptors select the scale byte of their 32-wide sub-block
-//   warps 2-3   scale loaders: each warp fills every other slot of the scale ring (eight K blocks per slot in a pair) with
-//               the scale bytes of this CTA's 128 A rows and of ALL 256 B rows of the tile (each CTA of a pair multiplies
-//               its A rows by every column, so it needs every column's scale), laid out in shared memory the way
-//               tcgen05.cp expects a 128-row group: byte offset (row % 32) * 16 + (row / 32) * 4 + sub-block. The loads
-//               of a slot are issued before the wait for the slot. In a pair the leader's one tcgen05.cp
-//               (cta_group::2) makes each CTA copy from its OWN shared memory into its own tensor memory
-//   warps 4-7   epilogue: tensor memory -> registers -> output type -> swizzled staging -> TMA store
+// Scale bytes. tcgen05.cp (32x128b.warpx4) copies one 512-byte atom — 128 rows x 4 scale bytes, byte offset
+// (row % 32) * 16 + (row / 32) * 4 — from shared memory into four tensor-memory columns. The row-major scale matrices
+// are therefore first rewritten by a small kernel (tile_scales_kernel, same stream, stream-ordered scratch memory) into
+// such atoms, one per group of 128 rows, K block and set of four bytes per row, and the product kernel fetches them by
+// TMA together with the operands. (Fetching and transposing them with loader warps inside the product kernel was the
+// first design; with 16 scale bytes per row and K block in NVFP4 those warps, competing with TMA and the tensor cores
+// for shared memory, set the kernel's pace: 0.80 ms against 0.69 at M = 8192, N = 28672, K = 8192.)
+//
+// Roles per CTA (192 threads, persistent over tiles):
+//   warp 0      TMA producer: per stage the A and B tiles (128 bytes of K per row; two K blocks per stage for MXFP8 —
+//               one barrier per 256 codes halves the issuing warp's polls and commits — one for the 4-bit formats) and
+//               the stage's scale atoms: this CTA's 128 A rows and ALL 256 B rows of the tile (each CTA of a pair
+//               multiplies its A rows by every column, so it needs every column's scale)
+//   warp 1      MMA issuer: per K block copies that block's scale atoms into tensor memory (tcgen05.cp; in a pair the
+//               leader's one instruction, cta_group::2, makes each CTA copy from its OWN shared memory into its own
+//               tensor memory) and issues four instructions (K = 32 codes for MXFP8, whose descriptors select the scale
+//               byte of their sub-block; 64 codes for the 4-bit formats)
+//   warps 2-5   epilogue: tensor memory -> registers -> output type -> swizzled staging -> TMA store
 //
 // Tensor memory (512 columns): 256 accumulator columns, then 4 columns of A scales and 8 of B scales. One accumulator
 // only — two would not leave room for the scales — so the epilogue's tensor-memory reads (not its stores) are not
@@ -46,9 +51,8 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 128;          // codes per stage row = four 32-wide scale blocks
-constexpr int kThreads = 256;
+constexpr int kThreads = 192;      // producer warp, issuing warp, four epilogue warps
 constexpr int kABytes = kBM * 128;
-constexpr int kScaleGroupBytes = 512 + 2 * 512;         // one set of scale copies: the A group, then two B groups of 128 rows
 constexpr int kEpilogueBytes = 4 * 2048;                // per epilogue warp: one 16-row x 128-byte store box
 constexpr int kMxfp8 = 0, kNvfp4 = 1, kMxfp4 = 2;  // FORMAT: what the codes and the scale bytes are
 
@@ -66,29 +70,19 @@ struct Layout {
   // flight (with two 64 KB stages only one is ever being filled, and the TMA round trip then sets the K-block rate): its
   // stages are single K blocks, five of them in a pair.
   static constexpr int kBlocksPerStage = FP4 ? 1 : 2;
-  // A pair's 4-bit kernel reads its scale bytes from a copy that a small kernel has laid out beforehand the way
-  // tcgen05.cp wants them: they then arrive by TMA with the operands, as part of the stage (one 512-byte atom per set).
-  static constexpr bool kPretiled = FP4 && CTA_GROUP == 2;
-  static constexpr int kStageScaleBytes = kPretiled ? 3 * kWordsPerBlock * 512 : 0;  // A rows, B rows 0-127, B rows 128-255
-  static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes + kStageScaleBytes;
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
-  // four instructions take four bytes each.
+  // four instructions take four bytes each, MXFP4's share a set in twos.
   static constexpr int kScaleSets = kWordsPerBlock;
-  static constexpr int kScaleBlockBytes = kScaleSets * kScaleGroupBytes;
-  // K blocks of scales per ring slot. An MXFP8 pair takes eight (32 scale bytes per row): the peer's loaders signal the
-  // leader with a cluster-scope release arrive, which costs on the order of a thousand cycles, and a slot has to hide
-  // that together with the global-memory latency behind the K blocks of the other slot; four were measured 17 %
-  // slower. NVFP4 has four times the scale bytes: four K blocks per slot in a pair (with one operand stage fewer to
-  // make room), two alone.
-  static constexpr int kScaleChunk = (CTA_GROUP == 2 ? 8 : 4) / (FORMAT == kNvfp4 ? 2 : 1);
-  static constexpr int kScaleSlotBytes = kScaleChunk * kScaleBlockBytes;
-  static constexpr int kStages = FP4 ? (kPretiled ? 5 : 4) : (CTA_GROUP == 2 ? 3 : 2);
-  // Scale ring slots: a third one for the NVFP4 pair, whose refill (global loads, shared-memory stores, the peer's
-  // cluster-scope arrive) does not fit behind one slot of four K blocks.
-  static constexpr int kScaleSlots = (FP4 && CTA_GROUP == 2) ? 3 : 2;
-  // the epilogue's staging buffers follow and are swizzled 128-byte rows: they start on a 1024-byte boundary
-  static constexpr int kScaleRingBytes = kPretiled ? 0 : (kScaleSlots * kScaleSlotBytes + 1023) / 1024 * 1024;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kEpilogueBytes + 256 + 1024;
+  // The scale bytes of a stage arrive with its operands, by TMA, from a copy that a small kernel has laid out beforehand
+  // the way tcgen05.cp wants them: 512-byte atoms (128 rows x 4 bytes), one per group of 128 rows, K block and set.
+  // Behind the operands a stage holds three runs of atoms — this CTA's A rows, B rows 0-127, B rows 128-255 of the tile
+  // (each CTA of a pair multiplies its A rows by every column, so it needs every column's scale) — each run with the
+  // atoms of the stage's K blocks in order.
+  static constexpr int kRunBytes = kBlocksPerStage * kScaleSets * 512;
+  static constexpr int kStageScaleBytes = 3 * kRunBytes;
+  static constexpr int kStageBytes = kBlocksPerStage * kBlockBytes + kStageScaleBytes;
+  static constexpr int kStages = FP4 ? (CTA_GROUP == 2 ? 5 : 4) : (CTA_GROUP == 2 ? 3 : 2);
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + 256 + 1024;
 };
 constexpr int kTmemColumns = 512;
 constexpr int kTmemScaleA = 256;                        // first column of the scale factors: per set, 4 columns of A
@@ -98,16 +92,11 @@ static_assert(Layout<1, kMxfp8>::kSmemBytes <= 232448 && Layout<2, kMxfp8>::kSme
               Layout<1, kMxfp4>::kSmemBytes <= 232448 && Layout<2, kMxfp4>::kSmemBytes <= 232448, "shared memory budget");
 
 struct MxScales {
-  const uint8_t* sa;  // [M, K / 32] e8m0, or [M, K / 16] e4m3 for NVFP4
-  const uint8_t* sb;  // [N, K / 32] e8m0, or [N, K / 16] e4m3
-  long long ldsa, ldsb;  // row pitches in bytes
-  int vector_ok;         // both addresses and pitches are multiples of 16: 16 scale bytes of a row come in one load
-  int b_atom0;           // 4-bit pair kernel: first 512-byte atom of B's scales in the pre-tiled copy (A's start at 0)
-  float alpha;           // NVFP4: product of the two tensor scales, applied to the finished accumulator
+  int b_atom0;  // first 512-byte atom of B's scales in the pre-tiled copy (A's atoms start at 0)
+  float alpha;  // NVFP4: product of the two tensor scales, applied to the finished accumulator
 };
 
-enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaScale = 43, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45,
-            kSiteScaleEmpty = 46 };
+enum Site { kSiteProducerEmpty = 41, kSiteMmaFull = 42, kSiteMmaTmemEmpty = 44, kSiteEpilogueFull = 45 };
 
 
 // Instruction descriptor of kind::mxf8f6f4.block_scale: B scale id [4,6), A format [7,10), B format [10,13), majors 15 /
@@ -209,15 +198,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   constexpr int kChunks = kBN / kChunkCols;
   using L = Layout<CTA_GROUP, FORMAT>;
   constexpr bool FP4 = L::FP4;
-  constexpr int kWordsPerBlock = L::kWordsPerBlock;
   constexpr int kStages = L::kStages;
   constexpr int kStageBytes = L::kStageBytes;
   constexpr int kBlockBytes = L::kBlockBytes;
-  constexpr int kScaleChunk = L::kScaleChunk;
-  constexpr int kScaleSlotBytes = L::kScaleSlotBytes;
-  constexpr int kScaleBlockBytes = L::kScaleBlockBytes;
-  constexpr int kScaleSlots = L::kScaleSlots;
   constexpr int kBlocksPerStage = L::kBlocksPerStage;
+  constexpr int kSets = L::kScaleSets;
+  constexpr int kRunBytes = L::kRunBytes;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -225,16 +211,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* smem = smem_raw + (base - raw);
 
   const uint32_t stages_addr = base;
-  const uint32_t scale_addr = base + kStages * kStageBytes;
-  const uint32_t epilogue_addr = scale_addr + L::kScaleRingBytes;
-  uint8_t* tail = smem + kStages * kStageBytes + L::kScaleRingBytes + kEpilogueBytes;
+  const uint32_t epilogue_addr = base + kStages * kStageBytes;
+  uint8_t* tail = smem + kStages * kStageBytes + kEpilogueBytes;
   const uint32_t full_bar = smem_u32(tail);                  // [kStages]
   const uint32_t empty_bar = full_bar + 8 * kStages;         // [kStages]
-  const uint32_t scale_full_bar = empty_bar + 8 * kStages;            // [kScaleSlots]
-  const uint32_t scale_empty_bar = scale_full_bar + 8 * kScaleSlots;  // [kScaleSlots]
-  const uint32_t tmem_full_bar = scale_empty_bar + 8 * kScaleSlots;
+  const uint32_t tmem_full_bar = empty_bar + 8 * kStages;
   const uint32_t tmem_empty_bar = tmem_full_bar + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2 * kScaleSlots + 2));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -250,11 +233,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
-    for (int s = 0; s < kScaleSlots; ++s) {
-      // one loader warp of every CTA of the tile fills a slot (both of them when the scale rows are only 4-byte aligned)
-      mbar_init(scale_full_bar + 8 * s, ((FP4 || scales.vector_ok) ? 1 : 2) * CTA_GROUP);
-      mbar_init(scale_empty_bar + 8 * s, 1);             // the issuing thread's commit
-    }
     mbar_init(tmem_full_bar, 1);
     mbar_init(tmem_empty_bar, 4 * CTA_GROUP);            // the epilogue warps of every CTA of the tile
     *abort_flag = 0;
@@ -262,7 +240,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
     prefetch_tensormap(&map_c);
-    if (L::kPretiled) prefetch_tensormap(&map_scales);
+    prefetch_tensormap(&map_scales);
   }
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(tmem_slot), kTmemColumns);
@@ -295,12 +273,22 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           const int blocks = min(kBlocksPerStage, num_kb - kb);  // an odd K-block count leaves the last stage half full
           const uint32_t dst = stages_addr + stage * kStageBytes;
+          // the stage's scale atoms, already in tcgen05.cp's layout (rows of the copy = atoms of 512 bytes): one run for
+          // this CTA's group of 128 A rows and one for each group of the tile's B rows. A run is always fetched whole;
+          // behind an odd last K block it ends with atoms that no instruction reads.
+          const uint32_t sdst = dst + kBlocksPerStage * kBlockBytes;
+          const int a_atom = ((tm * CTA_GROUP + int(rank)) * num_kb + kb) * kSets;
+          const int b_atom = scales.b_atom0 + (tn * 2 * num_kb + kb) * kSets;
           if constexpr (CTA_GROUP == 1) {
-            mbar_arrive_expect_tx(full_bar + 8 * stage, uint32_t(blocks) * kBlockBytes);
+            const uint32_t full = full_bar + 8 * stage;
+            mbar_arrive_expect_tx(full, uint32_t(blocks) * kBlockBytes + L::kStageScaleBytes);
             for (int j = 0; j < blocks; ++j) {
-              tma_load_2d(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, full_bar + 8 * stage);
-              tma_load_2d(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, full_bar + 8 * stage);
+              tma_load_2d(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, full);
+              tma_load_2d(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, full);
             }
+            tma_load_2d(sdst, &map_scales, 0, a_atom, full);
+            tma_load_2d(sdst + kRunBytes, &map_scales, 0, b_atom, full);
+            tma_load_2d(sdst + 2 * kRunBytes, &map_scales, 0, b_atom + num_kb * kSets, full);
           } else {
             // both CTAs' tiles complete on the leader's barrier; the leader alone arms it for both
             if (rank == 0) {
@@ -311,17 +299,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               tma_load_2d_pair(dst + j * kBlockBytes, &map_a, (kb + j) * kBK, row_a, leader_full);
               tma_load_2d_pair(dst + j * kBlockBytes + kABytes, &map_b, (kb + j) * kBK, row_b, leader_full);
             }
-            if constexpr (L::kPretiled) {
-              // this K block's scale atoms, already in tcgen05.cp's layout: this CTA's group of 128 A rows and both
-              // groups of the tile's B rows (rows of the copy = atoms of 512 bytes, one per 128-row group, K block and set)
-              constexpr int kSets = L::kScaleSets;
-              const uint32_t sdst = dst + kBlockBytes;
-              const int a_atom = ((tm * CTA_GROUP + int(rank)) * num_kb + kb) * kSets;
-              const int b_atom = scales.b_atom0 + (tn * 2 * num_kb + kb) * kSets;
-              tma_load_2d_pair(sdst, &map_scales, 0, a_atom, leader_full);
-              tma_load_2d_pair(sdst + kSets * 512, &map_scales, 0, b_atom, leader_full);
-              tma_load_2d_pair(sdst + 2 * kSets * 512, &map_scales, 0, b_atom + num_kb * kSets, leader_full);
-            }
+            tma_load_2d_pair(sdst, &map_scales, 0, a_atom, leader_full);
+            tma_load_2d_pair(sdst + kRunBytes, &map_scales, 0, b_atom, leader_full);
+            tma_load_2d_pair(sdst + 2 * kRunBytes, &map_scales, 0, b_atom + num_kb * kSets, leader_full);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -343,7 +323,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t desc_hi = uint32_t(desc0 >> 32);
       int stage = 0;
       uint32_t phase = 0, iter = 0;
-      uint32_t slot = 0, slot_phase = 0;  // position in the ring of scale slots
       bool ok = true;
       // This thread is the kernel's critical path: every tcgen05 instruction it issues costs about 60 cycles and a
       // barrier poll about 220 even when it succeeds at once (cycle trace with one K block per barrier: 851 cycles per K
@@ -362,25 +341,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int blocks = min(kBlocksPerStage, num_kb - kb0);
           for (int j = 0; j < blocks && ok; ++j) {
             const int kb = kb0 + j;
-            const int in_chunk = kb & (kScaleChunk - 1);
-            if constexpr (!L::kPretiled) {
-              if (in_chunk == 0) {
-                if (!wait(scale_full_bar + 8 * slot, slot_phase, kSiteMmaScale)) {
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-              }
-            }
-            const bool slot_done = !L::kPretiled && (in_chunk == kScaleChunk - 1 || kb == num_kb - 1);
-            // where this K block's scale groups lie: in the ring slot (sets 1536 bytes apart, each A | B | B), or, for
-            // the pre-tiled copy, behind the stage's operands (A's sets, then the sets of each group of B rows)
-            const uint32_t in_stage = stages_addr + stage * kStageBytes + kBlockBytes;
-            const uint32_t block = scale_addr + slot * kScaleSlotBytes + in_chunk * kScaleBlockBytes;
-            const uint32_t group_a = L::kPretiled ? in_stage : block;
-            const uint32_t group_b0 = L::kPretiled ? in_stage + L::kScaleSets * 512 : block + 512;
-            const uint32_t group_b1 = L::kPretiled ? in_stage + 2 * L::kScaleSets * 512 : block + 1024;
-            constexpr uint32_t kSetStride = L::kPretiled ? 512 : kScaleGroupBytes;
+            // this K block's scale atoms behind the stage's operands: A's sets, then the sets of each group of B rows
+            const uint32_t group_a = stages_addr + stage * kStageBytes + kBlocksPerStage * kBlockBytes + j * (kSets * 512);
+            const uint32_t group_b0 = group_a + kRunBytes, group_b1 = group_a + 2 * kRunBytes;
+            constexpr uint32_t kSetStride = 512;
             if (leader) {
               const uint32_t a_lo = uint32_t(desc0) + ((stage * kStageBytes + j * kBlockBytes) >> 4);
               const uint32_t b_lo = a_lo + (kABytes >> 4);
@@ -418,16 +382,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                        sfb, (kb > 0 || ks > 0) ? 1u : 0u);
                 }
               }
-              if (slot_done) {
-                if constexpr (CTA_GROUP == 1) {
-                  umma_commit(scale_empty_bar + 8 * slot);
-                } else {
-                  umma_commit_pair(scale_empty_bar + 8 * slot, 0x3);
-                }
-              }
             }
             __syncwarp();
-            if (slot_done && ++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
           }
           if (!ok) break;
           if (leader) {
@@ -454,155 +410,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         __syncwarp();
       }
     }
-  } else if (warp < 4) {
-    // ---------------------------------------------------------------- scale loaders (two warps)
-    // Per ring slot: the scale bytes of this CTA's 128 A rows and the tile's 256 B rows, 384 rows. Rows beyond the matrix
-    // get the code of 1.0 (their codes are zero-filled by TMA, the product stays zero).
-    const int tid = int(threadIdx.x) - 64;
-    const uint32_t leader_scale_full = CTA_GROUP == 2 ? map_to_cta(scale_full_bar, 0) : scale_full_bar;
-    if constexpr (L::kPretiled) {
-      // nothing to load: the scale atoms of a K block arrive with its operands (the producer warp's TMA)
-    } else if (FP4 || scales.vector_ok) {
-      // Filling a ring slot is a chain — 16-byte loads (1000-1500 cycles), stores, proxy fence, cluster-scope arrive
-      // (about 1000) — and a trace of the issuing warp showed it waiting for scale factors 2000-2900 cycles of every
-      // slot when both loader warps worked on every slot one after the other. So the two loader warps take ALTERNATE
-      // slots, each filling its slot with all 384 rows (twelve per lane), and they issue the loads before they wait for
-      // the slot: a slot then costs a warp max(load latency, wait) + stores + arrive once per two slots.
-      // A row's bytes for one slot are contiguous: word k belongs to K block k of the slot (MXFP8: one word = the four
-      // 32-wide sub-blocks of a K block) or to instruction k % 4 of K block k / 4 (NVFP4: one word = the four 16-wide
-      // blocks of a 64-code instruction). Lane s of a 128-row group's pass takes row (s % 4) * 32 + s / 4, whose place in
-      // the tcgen05.cp layout is word s: a warp's stores fall on consecutive words.
-      constexpr int kWords = kScaleChunk * kWordsPerBlock;  // 32-bit words of scale bytes per row and slot
-      constexpr uint32_t kUnit = FORMAT == kNvfp4 ? 0x38383838u : 0x7f7f7f7fu;  // the code of 1.0 (e4m3 / e8m0), for rows beyond the matrix
-      const int mine = warp - 2;
-      uint32_t slot = 0, slot_phase = 0;
-      int chunk_index = 0;
-      for (int t = first_tile; t < num_tiles; t += tile_step) {
-        int tm, tn;
-        tile_coords(t, p, tm, tn);
-        bool ok = true;
-        for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk, ++chunk_index) {
-          if ((chunk_index & 1) != mine) {
-            if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
-            continue;
-          }
-          uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-          const int words_here = min(kScaleChunk, num_kb - kb0) * kWordsPerBlock;
-          uint32_t w[12][kWords];
-#pragma unroll
-          for (int i = 0; i < 12; ++i) {
-            const int group = i >> 2;                      // 0: A rows, 1 / 2: B rows 0-127 / 128-255
-            const int s_index = (i & 3) * 32 + int(lane);
-            const int q = (s_index & 3) * 32 + (s_index >> 2);
-            const bool is_a = group == 0;
-            const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + q
-                                       : (long long)tn * kBN + (group - 1) * 128 + q;
-            const bool live = row < (is_a ? p.m : p.n);
-            const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) +
-                                 (long long)kb0 * (4 * kWordsPerBlock);
-            if (live && words_here == kWords) {
-              // the common case, kept lean: this warp's instruction count is what the slot's turn-around is made of
-#pragma unroll
-              for (int v = 0; v < kWords / 4; ++v) {
-                const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
-                w[i][4 * v] = x.x, w[i][4 * v + 1] = x.y, w[i][4 * v + 2] = x.z, w[i][4 * v + 3] = x.w;
-              }
-            } else {
-              // a row beyond the matrix (the code of 1.0 everywhere) or the last, shorter slot of a row
-#pragma unroll
-              for (int k = 0; k < kWords; ++k) {
-                w[i][k] = kUnit;
-                if (live && k < words_here) w[i][k] = __ldg(reinterpret_cast<const uint32_t*>(src) + k);
-              }
-            }
-          }
-          if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
-                                                 kSiteScaleEmpty))) {
-            ok = false;
-            break;
-          }
-#pragma unroll
-          for (int i = 0; i < 12; ++i) {
-            uint8_t* dst = slot_base + (i >> 2) * 512 + ((i & 3) * 32 + int(lane)) * 4;
-#pragma unroll
-            for (int k = 0; k < kWords; ++k) {
-              const int block = k / kWordsPerBlock, set = k % kWordsPerBlock;
-              *reinterpret_cast<uint32_t*>(dst + block * kScaleBlockBytes + set * kScaleGroupBytes) = w[i][k];
-            }
-          }
-          fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CTA_GROUP == 2) {
-              mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
-            } else {
-              mbar_arrive(scale_full_bar + 8 * slot);
-            }
-          }
-          if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
-        }
-        if (!ok) break;
-      }
-    } else {
-      // MXFP8 scale rows that are only 4-byte aligned: both warps fill every slot with word loads
-      uint32_t slot = 0, slot_phase = 0;
-      bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
-        int tm, tn;
-        tile_coords(t, p, tm, tn);
-        for (int kb0 = 0; kb0 < num_kb; kb0 += kScaleChunk) {
-          const int blocks_here = min(kScaleChunk, num_kb - kb0);
-          if (!__all_sync(0xffffffffu, mbar_wait(scale_empty_bar + 8 * slot, slot_phase ^ 1u, abort_flag, status,
-                                                 kSiteScaleEmpty))) {
-            ok = false;
-            break;
-          }
-          uint8_t* slot_base = smem + kStages * kStageBytes + slot * kScaleSlotBytes;
-#pragma unroll
-          for (int i = 0; i < 6; ++i) {
-            const int r = tid + i * 64;  // 0..127: A rows, 128..383: B rows
-            const bool is_a = r < kBM;
-            const int local = is_a ? r : r - kBM;
-            const long long row = is_a ? (long long)tm * (kBM * CTA_GROUP) + int(rank) * kBM + local
-                                       : (long long)tn * kBN + local;
-            const bool live = row < (is_a ? p.m : p.n);
-            const int group = is_a ? 0 : 1 + local / 128;
-            const int in_group = local & 127;
-            uint8_t* dst = slot_base + group * 512 + (in_group & 31) * 16 + (in_group >> 5) * 4;
-            uint32_t w[kScaleChunk];
-#pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) w[j] = 0x7f7f7f7fu;
-            if (live) {
-              const uint8_t* src = (is_a ? scales.sa + row * scales.ldsa : scales.sb + row * scales.ldsb) + kb0 * 4;
-              if (blocks_here == kScaleChunk && scales.vector_ok) {
-#pragma unroll
-                for (int q = 0; q < kScaleChunk / 4; ++q) {
-                  const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + q);
-                  w[4 * q] = v.x, w[4 * q + 1] = v.y, w[4 * q + 2] = v.z, w[4 * q + 3] = v.w;
-                }
-              } else {
-                for (int j = 0; j < blocks_here; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < kScaleChunk; ++j) *reinterpret_cast<uint32_t*>(dst + j * kScaleBlockBytes) = w[j];
-          }
-          fence_async_smem();  // generic-proxy writes must be visible to tcgen05.cp (async proxy)
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CTA_GROUP == 2) {
-              mbar_arrive_cluster(leader_scale_full + 8 * slot);  // release at cluster scope: the leader issues the copy
-            } else {
-              mbar_arrive(scale_full_bar + 8 * slot);
-            }
-          }
-          if (++slot == kScaleSlots) slot = 0, slot_phase ^= 1u;
-        }
-      }
-    }
   } else {
     // ---------------------------------------------------------------- epilogue warps
-    const int quarter = warp & 3;  // the 32-lane slice of tensor memory this warp may read
+    const int quarter = warp & 3;  // the 32-lane slice of tensor memory this warp may read (warps 2-5: slices 2, 3, 0, 1)
     const uint32_t buffer = epilogue_addr + quarter * 2048;
     const uint32_t leader_tmem_empty = CTA_GROUP == 2 ? map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
     uint32_t iter = 0;
@@ -747,6 +557,8 @@ tile_scales_kernel(const uint8_t* __restrict__ src, long long ld, long long rows
     if constexpr (SETS == 4) {
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(from));
       words[0] = v.x, words[1] = v.y, words[2] = v.z, words[3] = v.w;
+    } else if constexpr (SETS == 1) {
+      words[0] = __ldg(reinterpret_cast<const uint32_t*>(from));
     } else {
       const uint2 v = __ldg(reinterpret_cast<const uint2*>(from));
       words[0] = v.x, words[1] = v.y;
@@ -804,8 +616,7 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || lda % 16 != 0 || ldb % 16 != 0 || (ldc * c_bytes) % 16 != 0) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "TMA needs 16-byte aligned base addresses and row pitches");
   }
-  const bool vector_ok = aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0;
-  if (FP4 && !vector_ok) {
+  if (FP4 && !(aligned16(sa) && aligned16(sb) && ldsa % 16 == 0 && ldsb % 16 == 0)) {
     return fail(KRN_B200_ERR_INVALID_ARGUMENT, "the scale matrices of a 4-bit product need 16-byte aligned addresses and row pitches "
                 "(a row's scale bytes are fetched as 16-byte vectors)");
   }
@@ -826,7 +637,7 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   p.tiles_m = int((m + kBM * group - 1) / (kBM * group));
   p.tiles_n = int((n + kBN - 1) / kBN);
   p.b_kn = 0;
-  MxScales scales = {sa, sb, ldsa, ldsb, vector_ok ? 1 : 0, 0, alpha};
+  MxScales scales = {0, alpha};
 
   CUtensorMap map_a, map_b, map_c;
   {
@@ -850,45 +661,43 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  CUtensorMap map_scales = {};
-  if (group == 1) return launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
-  if constexpr (!FP4) {
-    return launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
-  } else {
-    // The 4-bit pair kernel reads its scale bytes from a copy in tcgen05.cp's layout, made here by a small kernel on the
-    // same stream: 512-byte atoms, one per group of 128 rows, K block and set, A's groups first (two per tile row,
-    // padded with zeros), then B's. The copy lives in stream-ordered memory for the length of the call.
-    constexpr int kSets = Layout<2, FORMAT>::kScaleSets;
-    const int num_kb = int(k_bytes / kBK);
-    const long long groups_a = 2LL * p.tiles_m, groups_b = 2LL * p.tiles_n;
-    const long long atoms_a = groups_a * num_kb * kSets, atoms_b = groups_b * num_kb * kSets;
-    if (num_kb > 65535 || atoms_a + atoms_b > INT32_MAX) {
-      return fail(KRN_B200_ERR_UNSUPPORTED, "a 4-bit product of this size is not available: its scale copy would have %lld "
-                  "atoms. Instead: split the product along M or N", atoms_a + atoms_b);
-    }
-    uint32_t* tiled = nullptr;
-    KRNB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&tiled), size_t(atoms_a + atoms_b) * 512, ctx->scratch_pool,
-                                      stream));
-    tile_scales_kernel<kSets><<<dim3(unsigned(groups_a), unsigned(num_kb)), 128, 0, stream>>>(sa, ldsa, m, num_kb, tiled);
-    tile_scales_kernel<kSets><<<dim3(unsigned(groups_b), unsigned(num_kb)), 128, 0, stream>>>(sb, ldsb, n, num_kb,
-                                                                                          tiled + atoms_a * 128);
-    int rc = KRN_B200_OK;
-    if (cudaError_t err = cudaGetLastError(); err != cudaSuccess) {
-      rc = fail(KRN_B200_ERR_CUDA, "launch of the scale layout kernel failed: %s", cudaGetErrorString(err));
-    }
-    if (rc == KRN_B200_OK) {
-      uint64_t dims[2] = {128, uint64_t(atoms_a + atoms_b)};
-      uint64_t strides[1] = {512};
-      uint32_t box[2] = {128, uint32_t(kSets)};
-      rc = encode_tensor_map(&map_scales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, tiled, dims, strides, box, Swizzle::kNone);
-    }
-    if (rc == KRN_B200_OK) {
-      scales.b_atom0 = int(atoms_a);
-      rc = launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
-    }
-    cudaFreeAsync(tiled, stream);  // after the product in stream order
-    return rc;
+  // The kernel reads its scale bytes from a copy in tcgen05.cp's layout, made here by a small kernel on the same
+  // stream: 512-byte atoms, one per group of 128 rows, K block and set; A's groups first (as many as the tiles cover,
+  // rows beyond the matrix as zeros), then B's. The copy lives in stream-ordered memory for the length of the call.
+  constexpr int kSets = Layout<1, FORMAT>::kScaleSets;
+  constexpr int kBlocksPerStage = Layout<1, FORMAT>::kBlocksPerStage;
+  const int num_kb = int(k_bytes / kBK);
+  const long long groups_a = (long long)group * p.tiles_m, groups_b = 2LL * p.tiles_n;
+  const long long atoms_a = groups_a * num_kb * kSets, atoms_b = groups_b * num_kb * kSets;
+  if (num_kb > 65535 || atoms_a + atoms_b > INT32_MAX) {
+    return fail(KRN_B200_ERR_UNSUPPORTED, "a block-scaled product of this size is not available: the copy of its scales "
+                "would have %lld atoms. Instead: split the product along M or N", atoms_a + atoms_b);
   }
+  uint32_t* tiled = nullptr;
+  KRNB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&tiled), size_t(atoms_a + atoms_b) * 512, ctx->scratch_pool,
+                                    stream));
+  tile_scales_kernel<kSets><<<dim3(unsigned(groups_a), unsigned(num_kb)), 128, 0, stream>>>(sa, ldsa, m, num_kb, tiled);
+  tile_scales_kernel<kSets><<<dim3(unsigned(groups_b), unsigned(num_kb)), 128, 0, stream>>>(sb, ldsb, n, num_kb,
+                                                                                        tiled + atoms_a * 128);
+  int rc = KRN_B200_OK;
+  if (cudaError_t err = cudaGetLastError(); err != cudaSuccess) {
+    rc = fail(KRN_B200_ERR_CUDA, "launch of the scale layout kernel failed: %s", cudaGetErrorString(err));
+  }
+  CUtensorMap map_scales;
+  if (rc == KRN_B200_OK) {
+    // one box = the atoms of one 128-row group for the K blocks of a stage
+    uint64_t dims[2] = {128, uint64_t(atoms_a + atoms_b)};
+    uint64_t strides[1] = {512};
+    uint32_t box[2] = {128, uint32_t(kBlocksPerStage * kSets)};
+    rc = encode_tensor_map(&map_scales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, tiled, dims, strides, box, Swizzle::kNone);
+  }
+  if (rc == KRN_B200_OK) {
+    scales.b_atom0 = int(atoms_a);
+    rc = group == 2 ? launch_for_output<2, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream)
+                    : launch_for_output<1, FORMAT>(ctx, c_type, map_a, map_b, map_c, map_scales, p, scales, stream);
+  }
+  cudaFreeAsync(tiled, stream);  // after the product in stream order
+  return rc;
 }
 
 }  // namespace
