@@ -42,7 +42,7 @@
 // product of the two matrices' f32 tensor scales (applied in the epilogue). Same kernel, same roles; what changes:
 // a 128-byte stage row is 256 codes, an instruction (kind::mxf4nvf4, scale_vec::4X) covers 64 codes and takes all four
 // bytes of a scale-factor column, so each of the four instructions of a K block has its own three scale copies and
-// its own twelve tensor-memory columns, and a row has 16 scale bytes per K block (one 16-byte load).
+// its own twelve tensor-memory columns, and a row has 16 scale bytes per K block (four atoms per group of 128 rows).
 #include "gemm_common.cuh"
 
 namespace krnb {
