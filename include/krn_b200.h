@@ -3,8 +3,12 @@
  * Every entry point is `extern "C"`, takes raw device addresses and 64-bit extents, enqueues work on the
  * caller's CUDA stream and returns without synchronising. The return value is a status code (0 = ok);
  * `krn_b200_last_error` gives the calling thread's message for the last non-zero status. Nothing here
- * allocates, frees or retains caller tensors. There is no CPU fallback: on a machine without a B200 the
- * compute entry points return KRN_B200_ERR_CUDA / KRN_B200_ERR_UNSUPPORTED.
+ * retains caller tensors, and nothing allocates device memory except the three products with tensor-core block scales
+ * (krn_b200_gemm_mxfp8_tn, krn_b200_gemm_nvfp4_tn, krn_b200_gemm_mxfp4_tn): each of their calls takes scratch memory the
+ * size of the two scale matrices from a stream-ordered pool the library keeps per device (cudaMallocFromPoolAsync on the
+ * caller's stream, cudaFreeAsync behind the product), so the driver's allocator is reached only the first time a size
+ * is seen. There is no CPU fallback: on a machine without a B200 the compute entry points return KRN_B200_ERR_CUDA /
+ * KRN_B200_ERR_UNSUPPORTED.
  *
  * The Python host reaches this file's functions through `krn_b200.hw.Libraries` and ctypes, the way the
  * reference reaches its compiled C programs (src/krn/runtime/cpu.py:168-175) — argument order below is the
@@ -155,7 +159,8 @@ int krn_b200_gemm_fp8_blockscaled_tn(int c_type, const void* a, const float* sa,
  * no partial sum is rescaled outside the unit.
  *   a, b    e4m3fn codes, K-major: a [M, K], b [N, K]; lda / ldb in elements, multiples of 16
  *   sa, sb  e8m0 bytes: sa [M, K / 32], sb [N, K / 32]; ldsa / ldsb row pitches in BYTES; addresses and pitches
- *           multiples of 4 (multiples of 16 let a row's scales of four K steps come in one load)
+ *           multiples of 4. A small kernel first rewrites both scale matrices into the 512-byte atoms tcgen05.cp copies
+ *           (128 rows x 4 bytes per K step), in scratch memory that lives for the call; the product fetches them by TMA
  *   K       a multiple of 128 (four scale blocks per step); M, N ragged as in krn_b200_gemm_tn
  *   c_type  KRN_B200_BF16, KRN_B200_F16 or KRN_B200_F32; ldc in elements */
 int krn_b200_gemm_mxfp8_tn(int c_type, const void* a, const uint8_t* sa, const void* b, const uint8_t* sb, void* c, int64_t m,

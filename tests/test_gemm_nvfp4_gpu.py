@@ -99,3 +99,27 @@ def test_quantised_containers_and_refusals(cuda) -> None:
     s = torch.zeros((128, 8), device="cuda", dtype=torch.uint8)
     with pytest.raises(Exception, match="K = 128 is not available on sm_100a"):
         calls.gemm_nvfp4_tn(a, s, a, s, torch.zeros((128, 128), device="cuda", dtype=torch.bfloat16))
+
+
+def test_calls_in_flight_on_two_streams_keep_their_own_scale_copies(cuda) -> None:
+    """Each call rewrites its scale bytes into scratch memory that lives for the call, in stream order. Calls of different
+    sizes queued back to back on two streams, with nothing waited for in between, must each read their own copy: every
+    result is compared with the oracle bit for bit (exactly representable inputs)."""
+    torch = cuda
+    rng = np.random.default_rng(77)
+    cases = []
+    for m, n, k in [(256, 512, 1024), (384, 256, 2048), (130, 264, 512), (512, 768, 1280)] * 3:
+        a_codes = o.e2m1_encode(rng.choice([-2.0, -1.0, 0.0, 0.5, 1.0, 3.0], (m, k)).astype(np.float32))
+        b_codes = o.e2m1_encode(rng.choice([-1.5, -1.0, 0.0, 0.5, 2.0, 4.0], (n, k)).astype(np.float32))
+        sa = o.e4m3_encode(np.exp2(rng.integers(-2, 3, (m, k // 16))).astype(np.float32))
+        sb = o.e4m3_encode(np.exp2(rng.integers(-2, 3, (n, k // 16))).astype(np.float32))
+        a, b = o.pack_nibbles(a_codes), o.pack_nibbles(b_codes)
+        dev = [torch.from_numpy(x).cuda() for x in (a, sa, b, sb)]
+        cases.append((a, sa, b, sb, dev, torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for i, (_, _, _, _, dev, c) in enumerate(cases):
+        calls.gemm_nvfp4_tn(dev[0], dev[1], dev[2], dev[3], c, 0.5, streams[i % 2])
+    torch.cuda.synchronize()
+    for a, sa, b, sb, _, c in cases:
+        np.testing.assert_array_equal(c.cpu().numpy(), o.gemm_nvfp4(a, sa, b, sb, 0.5, c_type=o.F32, threads=8))
