@@ -27,6 +27,9 @@
 //     exist so that no CTA is spent on a chunk beyond a context: 141 us — relaunching a CTA per unit costs less than
 //     the per-unit bookkeeping, and the hardware scheduler already keeps every slot busy;
 //   * a bounds report or a shared-memory flag inside the loop of the thread that issues the copies: +31 / +15 us.
+//   * the next iteration's score MMA issued behind this iteration's PV MMA under one commit: +7 us (the wait for the next
+//     K tile moves forward and the prefetch distance shrinks); the same with separate K and V barriers and K refetched as
+//     soon as the scores are formed: +3 us; chunks as the slowest grid dimension (short last chunks in the last wave): +5 us.
 //
 // The reference has no implementation of paged decode attention (its roadmap lists it); the arithmetic follows
 // its flash-attention statements (examples/04_libraries/08_flash_attention.py:44-59) with K, V = code * scale.
