@@ -66,9 +66,8 @@ struct Layout {
   static constexpr int kBRows = kBN / CTA_GROUP;           // rows of B this CTA loads
   static constexpr int kBlockBytes = kABytes + kBRows * 128;  // one K block (128 bytes per row): this CTA's A and B rows
   // A stage is two K blocks behind ONE barrier for MXFP8 (one poll and one commit of the issuing warp per 256 codes).
-  // NVFP4 has four times the scale bytes to keep in shared memory, and what its speed needs first is operand bytes in
-  // flight (with two 64 KB stages only one is ever being filled, and the TMA round trip then sets the K-block rate): its
-  // stages are single K blocks, five of them in a pair.
+  // The 4-bit formats run a K block in about the time of one TMA round trip, so what their speed needs first is stages
+  // in flight: theirs are single K blocks, five of them in a pair (three were measured to starve the issuing warp).
   static constexpr int kBlocksPerStage = FP4 ? 1 : 2;
   // Sets of scale copies per K block: MXFP8's four instructions share one (each picks its byte of the column), NVFP4's
   // four instructions take four bytes each, MXFP4's share a set in twos.
