@@ -541,31 +541,46 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
-// Scale bytes of one operand, row-major [rows, num_kb * 4 * SETS], into tcgen05.cp's layout: per group of 128 rows, K
-// block and set one atom of 128 words, word (row % 32) * 4 + row / 32 = the set's four scale bytes of that row. Thread t
-// of a block takes row (t % 4) * 32 + t / 4 of the group, whose word is word t: the stores of a warp are contiguous.
-// Rows beyond the matrix become zeros (their codes are zero-filled by TMA).
+// Scale bytes of both operands, row-major [rows, num_kb * 4 * SETS], into tcgen05.cp's layout: per group of 128 rows, K
+// block and set one atom of 128 words, word (row % 32) * 4 + row / 32 = the set's four scale bytes of that row. A block
+// takes one group of 128 rows (A's groups first, then B's) and kTileScalesBlocks K blocks; thread t takes row
+// (t % 4) * 32 + t / 4 of the group, whose word is word t: the loads of a thread are contiguous, the stores of a warp
+// are. Rows beyond the matrix become zeros (their codes are zero-filled by TMA).
+constexpr int kTileScalesBlocks = 8;
+
 template <int SETS>
 __global__ void __launch_bounds__(128)
-tile_scales_kernel(const uint8_t* __restrict__ src, long long ld, long long rows, int num_kb, uint32_t* __restrict__ out) {
-  const int group = blockIdx.x, kb = blockIdx.y, t = threadIdx.x;
-  const long long row = (long long)group * 128 + (t & 3) * 32 + (t >> 2);
-  uint32_t words[SETS] = {};
-  if (row < rows) {
-    const uint8_t* from = src + row * ld + (long long)kb * (4 * SETS);
-    if constexpr (SETS == 4) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(from));
-      words[0] = v.x, words[1] = v.y, words[2] = v.z, words[3] = v.w;
-    } else if constexpr (SETS == 1) {
-      words[0] = __ldg(reinterpret_cast<const uint32_t*>(from));
-    } else {
-      const uint2 v = __ldg(reinterpret_cast<const uint2*>(from));
-      words[0] = v.x, words[1] = v.y;
+tile_scales_kernel(const uint8_t* __restrict__ sa, long long ldsa, long long rows_a, int groups_a,
+                   const uint8_t* __restrict__ sb, long long ldsb, long long rows_b, int num_kb, uint32_t* __restrict__ out) {
+  const int group = blockIdx.x, kb0 = blockIdx.y * kTileScalesBlocks, t = threadIdx.x;
+  const bool of_a = group < groups_a;
+  const long long row = (long long)(of_a ? group : group - groups_a) * 128 + (t & 3) * 32 + (t >> 2);
+  const bool live = row < (of_a ? rows_a : rows_b);
+  const uint8_t* from = (of_a ? sa + row * ldsa : sb + row * ldsb) + (long long)kb0 * (4 * SETS);
+  uint32_t* to = out + ((long long)group * num_kb + kb0) * (SETS * 128) + t;  // B's atoms follow A's
+  const int count = min(kTileScalesBlocks, num_kb - kb0);
+  uint32_t words[kTileScalesBlocks][SETS] = {};
+#pragma unroll
+  for (int j = 0; j < kTileScalesBlocks; ++j) {
+    if (live && j < count) {
+      if constexpr (SETS == 4) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(from) + j);
+        words[j][0] = v.x, words[j][1] = v.y, words[j][2] = v.z, words[j][3] = v.w;
+      } else if constexpr (SETS == 1) {
+        words[j][0] = __ldg(reinterpret_cast<const uint32_t*>(from) + j);
+      } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(from) + j);
+        words[j][0] = v.x, words[j][1] = v.y;
+      }
     }
   }
-  uint32_t* to = out + ((long long)group * num_kb + kb) * (SETS * 128) + t;
 #pragma unroll
-  for (int set = 0; set < SETS; ++set) to[set * 128] = words[set];
+  for (int j = 0; j < kTileScalesBlocks; ++j) {
+    if (j < count) {
+#pragma unroll
+      for (int set = 0; set < SETS; ++set) to[(j * SETS + set) * 128] = words[j][set];
+    }
+  }
 }
 
 template <int CTA_GROUP, int FORMAT, typename OutT, bool OUT_BF16>
@@ -660,7 +675,7 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
     uint32_t box[2] = {uint32_t(128 / c_bytes), 16};
     if (int rc = encode_tensor_map(&map_c, c_dt, 2, c, dims, strides, box, Swizzle::k128B)) return rc;
   }
-  // The kernel reads its scale bytes from a copy in tcgen05.cp's layout, made here by a small kernel on the same
+  // The kernel reads its scale bytes from a copy in tcgen05.cp's layout, made here by one small kernel on the same
   // stream: 512-byte atoms, one per group of 128 rows, K block and set; A's groups first (as many as the tiles cover,
   // rows beyond the matrix as zeros), then B's. The copy lives in stream-ordered memory for the length of the call.
   constexpr int kSets = Layout<1, FORMAT>::kScaleSets;
@@ -675,9 +690,8 @@ int block_scaled_product(int c_type, const void* a, const uint8_t* sa, const voi
   uint32_t* tiled = nullptr;
   KRNB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&tiled), size_t(atoms_a + atoms_b) * 512, ctx->scratch_pool,
                                     stream));
-  tile_scales_kernel<kSets><<<dim3(unsigned(groups_a), unsigned(num_kb)), 128, 0, stream>>>(sa, ldsa, m, num_kb, tiled);
-  tile_scales_kernel<kSets><<<dim3(unsigned(groups_b), unsigned(num_kb)), 128, 0, stream>>>(sb, ldsb, n, num_kb,
-                                                                                        tiled + atoms_a * 128);
+  tile_scales_kernel<kSets><<<dim3(unsigned(groups_a + groups_b), unsigned((num_kb + kTileScalesBlocks - 1) / kTileScalesBlocks)),
+                              128, 0, stream>>>(sa, ldsa, m, int(groups_a), sb, ldsb, n, num_kb, tiled);
   int rc = KRN_B200_OK;
   if (cudaError_t err = cudaGetLastError(); err != cudaSuccess) {
     rc = fail(KRN_B200_ERR_CUDA, "launch of the scale layout kernel failed: %s", cudaGetErrorString(err));
