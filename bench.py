@@ -433,8 +433,20 @@ class GemmMxfp8(Workload):
 
     kernel_only = step
 
+    form = "mxfp8"  # the block format's name for krn_b200.streaming.StreamedScaledProduct
+
     def host_buffers(self):
-        raise RuntimeError("no host-operand streaming class exists for the MXFP8 product")
+        """End to end = `krn_b200.streaming.StreamedScaledProduct` over pinned host codes, scale bytes and output."""
+        from krn_b200 import streaming
+
+        torch = self.torch
+        self.host_in = [t.view(torch.uint8).cpu().pin_memory() for t in (self.a, self.sa, self.b, self.sb)]
+        self.host_out = torch.empty(self.c.shape, dtype=self.c.dtype).pin_memory()
+        self.streamed = streaming.StreamedScaledProduct(self.form, self.m, self.n, self.k, self.c.dtype)
+        return (sum(t.numel() * t.element_size() for t in self.host_in), self.host_out.numel() * self.host_out.element_size())
+
+    def e2e_step(self, calls) -> None:
+        self.streamed.run(*self.host_in, self.host_out, getattr(self, "alpha", 1.0))
 
     def parity_sample(self, oracle, calls) -> dict:
         import numpy as np
@@ -473,6 +485,7 @@ class GemmNvfp4(GemmMxfp8):
     per matrix) at the C3 extents M=8192 N=28672 K=8192 (seed 2), bf16 out. One GPU only."""
 
     name, metric, dtype = "gemm_nvfp4", "nvfp4_gemm_tflops", "fp4_e2m1"
+    form = "nvfp4"
     description = "NVFP4 GEMM M=8192 N=28672 K=8192, e4m3 scales per 1x16 block fed to the block-scaled MMA, bf16 out (seed 2)"
 
     def __init__(self, torch, rank, world, size=None) -> None:

@@ -202,6 +202,56 @@ class StreamedFp8Product:
         current.wait_stream(s.d2h)
 
 
+class StreamedScaledProduct:
+    """The MXFP8 / NVFP4 / MXFP4 product (block scales applied by the tensor cores) with host operands: codes and scale
+    bytes of `a` go first, then row panels of `b` (codes + their scale rows, panel boundaries on multiples of 256 rows);
+    column slabs of `c` return as they finish. `form` is "mxfp8", "nvfp4" or "mxfp4"; codes and scales are uint8 tensors
+    as `krn_b200.ops.quantize` lays them out (4-bit codes two per byte)."""
+
+    FORMS = {"mxfp8": (1, 32), "nvfp4": (2, 16), "mxfp4": (2, 32)}  # codes per byte, codes per scale byte
+
+    def __init__(self, form: str, m: int, n: int, k: int, out_dtype: Any, panels: int = 16) -> None:
+        torch = _torch()
+        if form not in self.FORMS:
+            raise ValueError(f"block format {form!r} is not available: use one of {sorted(self.FORMS)}")
+        per_byte, per_scale = self.FORMS[form]
+        self.form, self.m, self.n, self.k = form, m, n, k
+        self.a = torch.empty((m, k // per_byte), device="cuda", dtype=torch.uint8)
+        self.sa = torch.empty((m, k // per_scale), device="cuda", dtype=torch.uint8)
+        self.b = torch.empty((n, k // per_byte), device="cuda", dtype=torch.uint8)
+        self.sb = torch.empty((n, k // per_scale), device="cuda", dtype=torch.uint8)
+        self.c = torch.empty((m, n), device="cuda", dtype=out_dtype)
+        self.ranges = _panels(n, panels, 256)
+        self.streams = _Streams()
+
+    def run(self, a_host: Any, sa_host: Any, b_host: Any, sb_host: Any, c_host: Any, alpha: float = 1.0) -> None:
+        """`alpha` (the product of the two tensor scales) applies to NVFP4 only."""
+        torch = _torch()
+        current = torch.cuda.current_stream()
+        s = self.streams
+        s.h2d.wait_stream(current)
+        with torch.cuda.stream(s.h2d):
+            self.a.copy_(a_host, non_blocking=True)
+            self.sa.copy_(sa_host, non_blocking=True)
+            for index, (lo, hi) in enumerate(self.ranges):
+                self.b[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
+                self.sb[lo:hi].copy_(sb_host[lo:hi], non_blocking=True)
+                s.event(2 * index).record(s.h2d)
+        for index, (lo, hi) in enumerate(self.ranges):
+            current.wait_event(s.event(2 * index))
+            if self.form == "mxfp8":
+                fp8 = torch.float8_e4m3fn
+                calls.gemm_mxfp8_tn(self.a.view(fp8), self.sa, self.b[lo:hi].view(fp8), self.sb[lo:hi], self.c[:, lo:hi], current)
+            elif self.form == "nvfp4":
+                calls.gemm_nvfp4_tn(self.a, self.sa, self.b[lo:hi], self.sb[lo:hi], self.c[:, lo:hi], alpha, current)
+            else:
+                calls.gemm_mxfp4_tn(self.a, self.sa, self.b[lo:hi], self.sb[lo:hi], self.c[:, lo:hi], current)
+            s.event(2 * index + 1).record(current)
+            s.d2h.wait_event(s.event(2 * index + 1))
+            _copy_out(c_host[:, lo:hi], self.c[:, lo:hi], s.d2h)
+        current.wait_stream(s.d2h)
+
+
 class ShardedStreamedFp8Product:
     """The column-sharded block-scaled FP8 product with host operands, as `ShardedStreamedProduct`: rank r copies only
     its M/G rows of `a` (codes and 1x128 scales), NCCL all-gathers both over NVLink, and the rank's rows of `b` (codes

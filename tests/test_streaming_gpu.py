@@ -71,3 +71,40 @@ def test_streamed_attention_equals_the_device_call(cuda) -> None:
     calls.attention_forward(q.cuda(), k.cuda(), v.cuda(), direct, scale, True)
     torch.cuda.synchronize()
     assert torch.equal(o_host, direct.cpu())
+
+
+@pytest.mark.parametrize("form", ["mxfp8", "nvfp4", "mxfp4"])
+def test_streamed_scaled_product_matches_the_resident_call(cuda, form) -> None:
+    """Host codes and scale bytes through `StreamedScaledProduct` (panels of b, column slabs of c) give the same bytes as
+    one call on device-resident operands."""
+    torch = cuda
+    from krn_b200.runtime import calls
+    from oracle import oracle as o
+
+    m, n, k = 384, 1280, 2048
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((m, k), np.float32)
+    y = rng.standard_normal((n, k), np.float32)
+    alpha = 1.0
+    if form == "mxfp8":
+        (a, sa), (b, sb) = o.quantize_mxfp8(x), o.quantize_mxfp8(y)
+    elif form == "nvfp4":
+        (a, sa, ta), (b, sb, tb) = o.quantize_nvfp4(x), o.quantize_nvfp4(y)
+        alpha = ta * tb
+    else:
+        (a, sa), (b, sb) = o.quantize_mxfp4(x), o.quantize_mxfp4(y)
+    host = [torch.from_numpy(np.ascontiguousarray(t).view(np.uint8)).pin_memory() for t in (a, sa, b, sb)]
+    out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    streamed = streaming.StreamedScaledProduct(form, m, n, k, torch.bfloat16, panels=4)
+    streamed.run(*host, out, alpha)
+    torch.cuda.synchronize()
+    dev = [t.cuda() for t in host]
+    want = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    if form == "mxfp8":
+        calls.gemm_mxfp8_tn(dev[0].view(torch.float8_e4m3fn), dev[1], dev[2].view(torch.float8_e4m3fn), dev[3], want)
+    elif form == "nvfp4":
+        calls.gemm_nvfp4_tn(dev[0], dev[1], dev[2], dev[3], want, alpha)
+    else:
+        calls.gemm_mxfp4_tn(dev[0], dev[1], dev[2], dev[3], want)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.cpu().view(torch.int16))
